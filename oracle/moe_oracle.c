@@ -1,0 +1,447 @@
+/* CPU ORACLE -- TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+ *
+ * A plain-C restatement of the reference's FP8 MoE prefill path, used only by tests/,
+ * by the smoke check and by the CPU-baseline leg of the benchmark to CHECK the CUDA
+ * kernel. Nothing in the product path may call into this file.
+ *
+ * Parity pin: the routing functions are checked against outputs of the reference's own
+ * torch routines (research_archive/ds3_acc.py:242-273 grouped sigmoid; validation/
+ * ep4_acc.py:353-356 softmax == topk of the logits) and the MoE arithmetic against the
+ * reference's fp64 oracle (validation/ep4_acc.py:183-217), both executed on CPU from the
+ * reference sources to generate the fixtures under tests/golden/.
+ *
+ * Each function cites the reference lines it restates (paths relative to the reference
+ * repository root; Q = kernel/qwen_tp/src/prefill_mono_final_nb.cu,
+ * EP = kernel/qwen_ep/src/prefill_mono_final_nb.cu).
+ *
+ * Geometry is a run-time argument here (the kernels fix it at compile time), so small
+ * golden cases and the full-size cases share one implementation.
+ */
+#include <float.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* ------------------------------------------------------------------ number formats */
+
+static float e4m3_lut[256];
+static int lut_ready = 0;
+
+static float e4m3_decode_slow(uint8_t b) {
+  const int s = b >> 7, e = (b >> 3) & 15, m = b & 7;
+  float v;
+  if (e == 15 && m == 7) return NAN; /* the only NaN of e4m3fn; there is no infinity */
+  if (e == 0) v = ldexpf((float)m, -9);
+  else v = ldexpf(1.0f + (float)m / 8.0f, e - 7);
+  return s ? -v : v;
+}
+
+static void ensure_lut(void) {
+  if (!lut_ready) {
+    for (int i = 0; i < 256; ++i) e4m3_lut[i] = e4m3_decode_slow((uint8_t)i);
+    lut_ready = 1;
+  }
+}
+
+float oracle_e4m3_decode(uint8_t b) {
+  ensure_lut();
+  return e4m3_lut[b];
+}
+
+/* float -> e4m3, round to nearest even, saturating to +-448 (what the CUDA conversion
+ * cvt.rn.satfinite.e4m3x2.f32 does; Q:1239, Q:721). */
+uint8_t oracle_e4m3_encode(float x) {
+  if (isnan(x)) return 0x7F;
+  const uint8_t sign = signbit(x) ? 0x80 : 0x00;
+  float a = fabsf(x);
+  if (a > 448.0f) a = 448.0f;
+  if (a < 0.015625f) { /* below the smallest normal 2^-6: multiples of 2^-9 */
+    const int q = (int)rintf(a * 512.0f);
+    return (uint8_t)(sign | q); /* q == 8 is exactly the smallest normal, code 0x08 */
+  }
+  int ex;
+  (void)frexpf(a, &ex); /* a = f * 2^ex, f in [0.5, 1) */
+  int e = ex - 1;        /* a = m * 2^e, m in [1, 2) */
+  const float m = ldexpf(a, -e);
+  int mant = (int)rintf((m - 1.0f) * 8.0f);
+  if (mant == 8) { mant = 0; e += 1; }
+  int code = ((e + 7) << 3) | mant;
+  if (code > 0x7E) code = 0x7E;
+  return (uint8_t)(sign | code);
+}
+
+static inline float bf16_to_float(uint16_t b) {
+  uint32_t u = (uint32_t)b << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+/* float -> bf16 round to nearest even (__float2bfloat16, Q:917, Q:1447). */
+static inline uint16_t float_to_bf16(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x0040u);
+  const uint32_t lsb = (u >> 16) & 1u;
+  u += 0x7FFFu + lsb;
+  return (uint16_t)(u >> 16);
+}
+
+uint16_t oracle_float_to_bf16(float f) { return float_to_bf16(f); }
+float oracle_bf16_to_float(uint16_t b) { return bf16_to_float(b); }
+
+/* ------------------------------------------------------------------ router arithmetic */
+
+/* exp() as a fixed sequence of IEEE fp32 operations, so that the GPU kernel and this
+ * checker produce identical bits: clamp to [-87, 88]; t = x*log2(e); n = rint(t);
+ * r = fma(n,-ln2_hi,x); r = fma(n,-ln2_lo,r); degree-5 Horner polynomial in fma;
+ * y = fma(p, r*r, r) + 1; result = y * 2^n. */
+float oracle_det_expf(float x) {
+  x = fminf(fmaxf(x, -87.0f), 88.0f);
+  const float t = x * 1.44269504088896341f;
+  const float n = rintf(t);
+  float r = fmaf(n, -0.693145751953125f, x);
+  r = fmaf(n, -1.42860682030941723e-6f, r);
+  float p = 1.9875691500e-4f;
+  p = fmaf(p, r, 1.3981999507e-3f);
+  p = fmaf(p, r, 8.3334519073e-3f);
+  p = fmaf(p, r, 4.1665795894e-2f);
+  p = fmaf(p, r, 1.6666665459e-1f);
+  p = fmaf(p, r, 5.0000001201e-1f);
+  const float z = r * r;
+  float y = fmaf(p, z, r);
+  y = y + 1.0f;
+  const int ni = (int)n;
+  uint32_t bits = (uint32_t)(ni + 127) << 23;
+  float scale;
+  memcpy(&scale, &bits, 4);
+  return y * scale;
+}
+
+static inline float det_sigmoidf(float v) { return 1.0f / (1.0f + oracle_det_expf(-v)); }
+
+/* Router top-k (Q:1025-1185; expert-parallel remap EP:1185-1207).
+ * mode 0: softmax; selection on the logits, weight exp(l - max)/sum.
+ * mode 1: sigmoid; selection on sigmoid + bias, weight the unbiased sigmoid.
+ * mode 2: mode 1 restricted to the topk_group best of n_group expert groups, a group's
+ *         score being the sum of its two best biased scores.
+ * Selection is in descending score order, ties to the lower expert id; a score that is
+ * not greater than -FLT_MAX (masked group, -inf, NaN) is never selected, and a slot with
+ * no selectable expert left gets id -1 and weight 0. Weights are divided by their sum
+ * (clamped at 1e-30). With expert_map != NULL ids_out holds map[global id] (-1 = not on
+ * this rank); the weights keep the global denominator. ids_global_out is optional. */
+void oracle_route(const float* logits, int T, int E, int top_k, int mode, const float* bias, int n_group,
+                  int topk_group, const int32_t* expert_map, int32_t* ids_out, float* weights_out,
+                  int32_t* ids_global_out) {
+#pragma omp parallel
+  {
+    float* sel = (float*)malloc(sizeof(float) * (size_t)E);
+    float* unb = (float*)malloc(sizeof(float) * (size_t)E);
+    char* used = (char*)malloc((size_t)E);
+#pragma omp for schedule(static)
+    for (int t = 0; t < T; ++t) {
+      const float* row = logits + (size_t)t * E;
+      float m = 0.f, s = 1.f;
+      if (mode == 0) {
+        m = row[0];
+        for (int e = 1; e < E; ++e) m = fmaxf(m, row[e]);
+        /* summation order of the kernel: lane l sums experts l, l+32, ... in ascending
+         * order, then a butterfly (xor 16, 8, 4, 2, 1) over the 32 lane sums */
+        float lane_sum[32];
+        for (int l = 0; l < 32; ++l) {
+          float a = 0.f;
+          for (int j = 0; l + 32 * j < E; ++j) a += oracle_det_expf(row[l + 32 * j] - m);
+          lane_sum[l] = a;
+        }
+        for (int off = 16; off > 0; off >>= 1) {
+          float nxt[32];
+          for (int l = 0; l < 32; ++l) nxt[l] = lane_sum[l] + lane_sum[l ^ off];
+          memcpy(lane_sum, nxt, sizeof(nxt));
+        }
+        s = lane_sum[0];
+        for (int e = 0; e < E; ++e) { sel[e] = row[e]; unb[e] = row[e]; }
+      } else {
+        for (int e = 0; e < E; ++e) {
+          const float sg = det_sigmoidf(row[e]);
+          unb[e] = sg;
+          sel[e] = bias ? (sg + bias[e]) : sg;
+        }
+        if (mode == 2) {
+          const int eg = E / n_group;
+          float gs[64];
+          char keep[64];
+          for (int g = 0; g < n_group; ++g) {
+            int i1 = -1;
+            float b1 = -FLT_MAX, b2 = -FLT_MAX;
+            for (int i = 0; i < eg; ++i) {
+              const float v = sel[g * eg + i];
+              if (v > -FLT_MAX && (i1 < 0 || v > b1)) { b1 = v; i1 = i; }
+            }
+            for (int i = 0; i < eg; ++i) {
+              const float v = sel[g * eg + i];
+              if (i != i1 && v > -FLT_MAX) b2 = fmaxf(b2, v);
+            }
+            gs[g] = (i1 < 0) ? -FLT_MAX : (b1 + b2);
+            keep[g] = 0;
+          }
+          for (int r = 0; r < topk_group; ++r) {
+            float gb = -FLT_MAX;
+            int gi = -1;
+            for (int g = 0; g < n_group; ++g)
+              if (!keep[g] && gs[g] > gb) { gb = gs[g]; gi = g; }
+            if (gi >= 0) keep[gi] = 1;
+          }
+          for (int g = 0; g < n_group; ++g)
+            if (!keep[g])
+              for (int i = 0; i < eg; ++i) sel[g * eg + i] = -FLT_MAX;
+        }
+      }
+      memset(used, 0, (size_t)E);
+      float wsum = 0.f;
+      float wk[64];
+      int idk[64];
+      for (int k = 0; k < top_k; ++k) {
+        int bi = -1;
+        float bv = -FLT_MAX;
+        for (int e = 0; e < E; ++e) {
+          const float v = sel[e];
+          if (!used[e] && v > -FLT_MAX && (bi < 0 || v > bv)) { bv = v; bi = e; }
+        }
+        float w = 0.f;
+        if (bi >= 0) {
+          used[bi] = 1;
+          w = (mode == 0) ? (oracle_det_expf(unb[bi] - m) / s) : unb[bi];
+        }
+        wsum += w;
+        wk[k] = w;
+        idk[k] = bi;
+      }
+      const float inv = 1.0f / fmaxf(wsum, 1e-30f);
+      for (int k = 0; k < top_k; ++k) {
+        int lid = idk[k];
+        if (ids_global_out) ids_global_out[(size_t)t * top_k + k] = idk[k];
+        if (expert_map) lid = (idk[k] >= 0) ? expert_map[idk[k]] : -1;
+        ids_out[(size_t)t * top_k + k] = lid;
+        weights_out[(size_t)t * top_k + k] = wk[k] * inv;
+      }
+    }
+    free(sel);
+    free(unb);
+    free(used);
+  }
+}
+
+/* Per-expert counts, exclusive offsets, and the STABLE counting sort of the flat slot
+ * index t*top_k+k by local expert id (Q:1171 histogram, Q:1292-1328 scan, Q:1335-1339
+ * scatter). The reference's order inside an expert segment depends on atomics; the stable
+ * order (ascending flat index) is the deterministic member of that family. Slots with a
+ * negative id (not owned under expert parallelism, EP:1373-1379) are left out. */
+void oracle_sort(const int32_t* ids, int T, int top_k, int n_local, int32_t* counts, int32_t* offsets,
+                 int32_t* sorted) {
+  const long n = (long)T * top_k;
+  memset(counts, 0, sizeof(int32_t) * (size_t)n_local);
+  for (long i = 0; i < n; ++i)
+    if (ids[i] >= 0 && ids[i] < n_local) counts[ids[i]] += 1;
+  offsets[0] = 0;
+  for (int e = 0; e < n_local; ++e) offsets[e + 1] = offsets[e] + counts[e];
+  int32_t* cur = (int32_t*)malloc(sizeof(int32_t) * (size_t)n_local);
+  memcpy(cur, offsets, sizeof(int32_t) * (size_t)n_local);
+  for (long i = 0; i < n; ++i)
+    if (ids[i] >= 0 && ids[i] < n_local) sorted[cur[ids[i]]++] = (int32_t)i;
+  free(cur);
+}
+
+/* bf16 -> e4m3 with one fp32 scale per (token, 128 columns) (Q:1225-1244):
+ * amax; amax < FLT_MIN -> 1; q = e4m3(x * (448/amax)); scale = amax/448. */
+void oracle_quant_act(const uint16_t* act_bf16, int T, int K, uint8_t* q_out, float* scale_out) {
+  const int nk = K / 128;
+#pragma omp parallel for schedule(static)
+  for (int t = 0; t < T; ++t) {
+    for (int kb = 0; kb < nk; ++kb) {
+      const uint16_t* src = act_bf16 + (size_t)t * K + kb * 128;
+      float am = 0.f;
+      for (int i = 0; i < 128; ++i) am = fmaxf(am, fabsf(bf16_to_float(src[i])));
+      if (am < FLT_MIN) am = 1.f;
+      const float inv = 448.0f / am;
+      for (int i = 0; i < 128; ++i) q_out[(size_t)t * K + kb * 128 + i] = oracle_e4m3_encode(bf16_to_float(src[i]) * inv);
+      scale_out[(size_t)t * nk + kb] = am / 448.0f;
+    }
+  }
+}
+
+/* ------------------------------------------------------------------ the expert path */
+
+static void decode_rows(const uint8_t* src, size_t n, float* dst) {
+  for (size_t i = 0; i < n; ++i) dst[i] = e4m3_lut[src[i]];
+}
+
+/* 128-term dot product in double (four fixed partial sums), rounded once to fp32 */
+static inline float dot128(const float* a, const float* b) {
+  double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+  for (int i = 0; i < 128; i += 4) {
+    s0 += (double)a[i] * (double)b[i];
+    s1 += (double)a[i + 1] * (double)b[i + 1];
+    s2 += (double)a[i + 2] * (double)b[i + 2];
+    s3 += (double)a[i + 3] * (double)b[i + 3];
+  }
+  return (float)((s0 + s1) + (s2 + s3));
+}
+
+/* Path-faithful expert computation for a list of tokens (same quantisation points and the
+ * same order of fp32 operations as the reference kernel):
+ *   up   (Q:572-664):  per 128-deep K slab d = sum a_q*w_q, acc += d * (w_scale * a_scale)
+ *   act  (Q:673-741):  v = up*gate / (1 + exp(-gate)); per (row,128 cols) amax;
+ *                      q = e4m3(v * 448/amax), scale = amax/448 (1/448 when amax == 0)
+ *   down (Q:799-926):  acc += d * (w_scale * inter_scale); partial = bf16(clamp(acc * route_w))
+ *   sum  (Q:1413-1452): out = bf16(sum_k float(partial_k) * out_scale (+ residual)), k ascending
+ * Slab dot products are taken in double and rounded once to fp32 (the tensor core's own
+ * fp32 summation order is not specified). ids are LOCAL expert ids; negative = skipped
+ * (EP:1459-1481).
+ *
+ * Layouts: w13 [n_local, 2*n_half, K] e4m3, gate rows then up rows; w13_scale
+ * [n_local, 2*n_half/128, K/128]; w2 [n_local, H, n_half]; w2_scale [n_local, H/128,
+ * n_half/128]. tokens[n_sel] lists the tokens to evaluate. Outputs: out_bf16 [n_sel, H];
+ * optional (may be NULL) partial_bf16 [n_sel*top_k, H], acc_dump [n_sel*top_k, 2*n_half]
+ * raw gate|up sums, inter_dump [n_sel*top_k, n_half] e4m3, iscale_dump [n_sel*top_k,
+ * n_half/128]; rows of skipped slots are zero-filled. */
+void oracle_moe_path(const int32_t* tokens, int n_sel, int top_k, int K, int H, int n_half, int n_local,
+                     const uint8_t* act_q, const float* act_scale, const int32_t* ids, const float* weights,
+                     const uint8_t* w13, const float* w13_scale, const uint8_t* w2, const float* w2_scale,
+                     float out_scale, const uint16_t* residual_bf16, uint16_t* out_bf16, uint16_t* partial_bf16,
+                     float* acc_dump, uint8_t* inter_dump, float* iscale_dump) {
+  ensure_lut();
+  const int nk = K / 128, np = n_half / 128, n_up = 2 * n_half;
+  const int n_pairs = n_sel * top_k;
+  uint16_t* partial = partial_bf16;
+  int own_partial = 0;
+  if (!partial) {
+    partial = (uint16_t*)calloc((size_t)n_pairs * H, sizeof(uint16_t));
+    own_partial = 1;
+  } else {
+    memset(partial, 0, (size_t)n_pairs * H * sizeof(uint16_t));
+  }
+  if (acc_dump) memset(acc_dump, 0, sizeof(float) * (size_t)n_pairs * n_up);
+  if (inter_dump) memset(inter_dump, 0, (size_t)n_pairs * n_half);
+  if (iscale_dump) memset(iscale_dump, 0, sizeof(float) * (size_t)n_pairs * np);
+
+  /* group the (token, slot) pairs by expert so each expert is decoded once */
+  int32_t* cnt = (int32_t*)calloc((size_t)n_local + 1, sizeof(int32_t));
+  for (int i = 0; i < n_sel; ++i)
+    for (int k = 0; k < top_k; ++k) {
+      const int e = ids[(size_t)tokens[i] * top_k + k];
+      if (e >= 0 && e < n_local) cnt[e + 1] += 1;
+    }
+  for (int e = 0; e < n_local; ++e) cnt[e + 1] += cnt[e];
+  int32_t* order = (int32_t*)malloc(sizeof(int32_t) * (size_t)(n_pairs > 0 ? n_pairs : 1));
+  int32_t* cur = (int32_t*)malloc(sizeof(int32_t) * (size_t)n_local);
+  memcpy(cur, cnt, sizeof(int32_t) * (size_t)n_local);
+  for (int i = 0; i < n_sel; ++i)
+    for (int k = 0; k < top_k; ++k) {
+      const int e = ids[(size_t)tokens[i] * top_k + k];
+      if (e >= 0 && e < n_local) order[cur[e]++] = i * top_k + k;
+    }
+
+#pragma omp parallel
+  {
+    float* w13f = (float*)malloc(sizeof(float) * (size_t)n_up * K);
+    float* w2f = (float*)malloc(sizeof(float) * (size_t)H * n_half);
+    float* af = (float*)malloc(sizeof(float) * (size_t)K);
+    float* gate = (float*)malloc(sizeof(float) * (size_t)n_half);
+    float* up = (float*)malloc(sizeof(float) * (size_t)n_half);
+    float* qf = (float*)malloc(sizeof(float) * (size_t)n_half);
+    float* isc = (float*)malloc(sizeof(float) * (size_t)np);
+#pragma omp for schedule(dynamic, 1)
+    for (int e = 0; e < n_local; ++e) {
+      if (cnt[e + 1] == cnt[e]) continue;
+      decode_rows(w13 + (size_t)e * n_up * K, (size_t)n_up * K, w13f);
+      decode_rows(w2 + (size_t)e * H * n_half, (size_t)H * n_half, w2f);
+      const float* s13 = w13_scale + (size_t)e * (n_up / 128) * nk;
+      const float* s2 = w2_scale + (size_t)e * (H / 128) * np;
+      for (int oi = cnt[e]; oi < cnt[e + 1]; ++oi) {
+        const int pair = order[oi];
+        const int t = tokens[pair / top_k], k = pair % top_k;
+        const float rw = weights[(size_t)t * top_k + k];
+        decode_rows(act_q + (size_t)t * K, (size_t)K, af);
+        const float* as = act_scale + (size_t)t * nk;
+        for (int n = 0; n < n_half; ++n) {
+          float ag = 0.f, au = 0.f;
+          const float* wg = w13f + (size_t)n * K;
+          const float* wu = w13f + (size_t)(n_half + n) * K;
+          for (int ks = 0; ks < nk; ++ks) {
+            const float sg = s13[(size_t)(n / 128) * nk + ks] * as[ks];
+            const float su = s13[(size_t)(np + n / 128) * nk + ks] * as[ks];
+            ag = fmaf(dot128(af + ks * 128, wg + ks * 128), sg, ag);
+            au = fmaf(dot128(af + ks * 128, wu + ks * 128), su, au);
+          }
+          gate[n] = ag;
+          up[n] = au;
+        }
+        if (acc_dump) {
+          memcpy(acc_dump + (size_t)pair * n_up, gate, sizeof(float) * (size_t)n_half);
+          memcpy(acc_dump + (size_t)pair * n_up + n_half, up, sizeof(float) * (size_t)n_half);
+        }
+        for (int b = 0; b < np; ++b) {
+          float mx = 0.f;
+          for (int i = 0; i < 128; ++i) {
+            const float g = gate[b * 128 + i];
+            const float v = (up[b * 128 + i] * g) / (1.0f + expf(-g));
+            up[b * 128 + i] = v;
+            mx = fmaxf(mx, fabsf(v));
+          }
+          const int nz = mx > FLT_MIN;
+          const float inv = nz ? (448.0f / mx) : 0.f;
+          isc[b] = nz ? (mx / 448.0f) : (1.0f / 448.0f);
+          for (int i = 0; i < 128; ++i) {
+            const uint8_t q = oracle_e4m3_encode(up[b * 128 + i] * inv);
+            qf[b * 128 + i] = e4m3_lut[q];
+            if (inter_dump) inter_dump[(size_t)pair * n_half + b * 128 + i] = q;
+          }
+          if (iscale_dump) iscale_dump[(size_t)pair * np + b] = isc[b];
+        }
+        for (int h = 0; h < H; ++h) {
+          float acc = 0.f;
+          const float* wr = w2f + (size_t)h * n_half;
+          for (int dk = 0; dk < np; ++dk) {
+            const float sc = s2[(size_t)(h / 128) * np + dk] * isc[dk];
+            acc = fmaf(dot128(qf + dk * 128, wr + dk * 128), sc, acc);
+          }
+          float v = acc * rw;
+          v = fminf(fmaxf(v, -3.38953139e38f), 3.38953139e38f);
+          partial[(size_t)pair * H + h] = float_to_bf16(v);
+        }
+      }
+    }
+    free(w13f); free(w2f); free(af); free(gate); free(up); free(qf); free(isc);
+  }
+
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < n_sel; ++i) {
+    const int t = tokens[i];
+    for (int h = 0; h < H; ++h) {
+      float s = 0.f;
+      for (int k = 0; k < top_k; ++k) {
+        const int e = ids[(size_t)t * top_k + k];
+        if (e >= 0 && e < n_local) s += bf16_to_float(partial[(size_t)(i * top_k + k) * H + h]);
+      }
+      float o;
+      if (residual_bf16) o = fmaf(s, out_scale, bf16_to_float(residual_bf16[(size_t)t * H + h]));
+      else o = s * out_scale;
+      out_bf16[(size_t)i * H + h] = float_to_bf16(o);
+    }
+  }
+  free(cnt); free(order); free(cur);
+  if (own_partial) free(partial);
+}
+
+int oracle_num_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}

@@ -1,0 +1,89 @@
+"""Compile the kernel once per geometry into unimonomoe_b200/lib/libprefill_mono_<variant>.so.
+
+The geometry of a binary is fixed at compile time and read back through its
+``prefill_wgmma_*`` accessors, as in the reference (kernel/build.sh:1-42, one variant per
+binary); here the variants share one source and differ by -D macros.
+
+    python -m unimonomoe_b200.build            # every variant
+    python -m unimonomoe_b200.build qwen_w1    # one
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIBDIR = os.path.join(HERE, "lib")
+
+QWEN = dict(K=2048, H=2048, MODE=0)
+DS = dict(K=7168, H=7168, MODE=2)
+
+# name -> geometry. N_HALF is this rank's slice of the expert intermediate width,
+# E_LOCAL the experts whose weights this rank holds.
+VARIANTS = {
+    "qwen_w1": dict(QWEN, N_HALF=512, E_LOCAL=256),   # Qwen3.5-35B-A3B-like, one GPU
+    "qwen_tp2": dict(QWEN, N_HALF=256, E_LOCAL=256),
+    "qwen_tp4": dict(QWEN, N_HALF=128, E_LOCAL=256),
+    "qwen_ep2": dict(QWEN, N_HALF=512, E_LOCAL=128),
+    "qwen_ep4": dict(QWEN, N_HALF=512, E_LOCAL=64),
+    "qwen_ep8": dict(QWEN, N_HALF=512, E_LOCAL=32),
+    "ds_tp8": dict(DS, N_HALF=256, E_LOCAL=256),      # DeepSeek-V3-like, 1/8 width shard
+    "ds_tp4": dict(DS, N_HALF=512, E_LOCAL=256),
+}
+
+SOURCES = ["mono_kernel.cu", "ptx_sm100.cuh", "bounded_wait.cuh", "route_math.cuh"]
+
+
+def lib_path(variant: str) -> str:
+    return os.path.join(LIBDIR, f"libprefill_mono_{variant}.so")
+
+
+def _stale(out: str) -> bool:
+    if not os.path.exists(out):
+        return True
+    t = os.path.getmtime(out)
+    return any(os.path.getmtime(os.path.join(CSRC, s)) > t for s in SOURCES) or os.path.getmtime(__file__) > t
+
+
+def build_variant(variant: str, force: bool = False, verbose: bool = False) -> str:
+    g = VARIANTS[variant]
+    out = lib_path(variant)
+    os.makedirs(LIBDIR, exist_ok=True)
+    if not force and not _stale(out):
+        return out
+    cmd = [
+        os.environ.get("NVCC", "nvcc"), "-O3", "-std=c++17",
+        "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "--expt-relaxed-constexpr",
+        "-Xptxas", "-v", "-shared", "-Xcompiler", "-fPIC",
+        f"-DMONO_K_DIM={g['K']}", f"-DMONO_H_DIM={g['H']}", f"-DMONO_N_HALF={g['N_HALF']}",
+        f"-DMONO_E_LOCAL={g['E_LOCAL']}", f"-DMONO_ROUTER_MODE={g['MODE']}",
+        os.path.join(CSRC, "mono_kernel.cu"), "-o", out,
+    ]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    log = r.stdout + r.stderr
+    with open(out + ".log", "w") as f:
+        f.write(" ".join(cmd) + "\n" + log)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {variant}:\n{log}")
+    if verbose:
+        for line in log.splitlines():
+            if "registers" in line or "spill" in line:
+                print(f"[{variant}] {line.strip()}")
+    return out
+
+
+def build_all(names=None, force: bool = False, verbose: bool = False) -> dict:
+    names = list(names or VARIANTS)
+    with ThreadPoolExecutor(max_workers=min(8, len(names))) as ex:
+        outs = list(ex.map(lambda n: build_variant(n, force, verbose), names))
+    return dict(zip(names, outs))
+
+
+if __name__ == "__main__":
+    sel = [a for a in sys.argv[1:] if not a.startswith("-")]
+    res = build_all(sel or None, force="--force" in sys.argv, verbose=True)
+    for k, v in res.items():
+        print(k, "->", v)

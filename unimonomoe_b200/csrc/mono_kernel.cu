@@ -1,0 +1,1241 @@
+// Single-launch FP8 MoE prefill layer for B200 (sm_100a): one persistent kernel, 148
+// CTAs (one per SM), phases separated by bounded software grid barriers.
+//
+//   phase 0   router top-k from fp32 logits (softmax, sigmoid+bias, or group-limited
+//             sigmoid+bias), per-warp expert histograms; bf16 -> e4m3 activation
+//             quantisation with one fp32 scale per (token, 128 columns)
+//   phase 1   prefix sum over experts, tile schedule, STABLE counting-sort scatter
+//   phase 2   per tile of <=128 sorted rows of one expert, warp-specialised:
+//               TMA warp      block-FP8 weight tiles -> shared memory (SWIZZLE_128B)
+//               gather warps  the tile's e4m3 activation rows -> shared memory (cp.async)
+//               MMA thread    tcgen05.mma kind::f8f6f4, M=128 N=256 K=32, one 128-deep
+//                             K slab at a time into one of two 256-column TMEM buffers
+//               8 epilogue warps  tcgen05.ld each slab, fold w_scale*a_scale into fp32
+//                             register accumulators, SiLU(gate)*up, requantise to e4m3
+//                             per (row,128) into shared memory, which the MMA thread
+//                             then uses as the A operand of the down projection; the
+//                             down result times the routing weight goes out as bf16
+//   phase 3   per token sum of its top-k partial rows -> bf16 [T,H]; under tensor
+//             parallelism the last `ncomm` CTAs instead run a chunked one-shot
+//             all-reduce through the NVLS multicast alias while the others compute.
+//
+// What it replaces in the reference (same semantics, different machine):
+//   kernel/qwen_tp/src/prefill_mono_final_nb.cu:932-1506 (device kernel),
+//   :1513-1791 (host launcher and accessors), kernel/qwen_ep/src/...:1185-1207,
+//   :1373-1379, :1459-1481 (expert-parallel ownership), kernel/deepseek_tp/src/...
+//   (geometry and router mode). Geometry is fixed at compile time through the MONO_*
+//   macros and read back through the prefill_wgmma_* accessors.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include <cfloat>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+
+#include "bounded_wait.cuh"
+#include "ptx_sm100.cuh"
+#include "route_math.cuh"
+
+#ifndef MONO_K_DIM
+#define MONO_K_DIM 2048
+#endif
+#ifndef MONO_H_DIM
+#define MONO_H_DIM 2048
+#endif
+#ifndef MONO_N_HALF
+#define MONO_N_HALF 512
+#endif
+#ifndef MONO_E_LOCAL
+#define MONO_E_LOCAL 256
+#endif
+#ifndef MONO_ROUTER_MODE
+#define MONO_ROUTER_MODE 0
+#endif
+
+namespace mono {
+namespace {
+
+// ------------------------------------------------------------------ geometry
+constexpr int E = kNumExperts;
+constexpr int E_LOCAL = MONO_E_LOCAL;
+constexpr bool EP_BUILD = (E_LOCAL != E);
+constexpr int TOP_K = 8;
+constexpr int K_DIM = MONO_K_DIM;
+constexpr int H_DIM = MONO_H_DIM;
+constexpr int N_HALF = MONO_N_HALF;
+constexpr int N_UP = 2 * N_HALF;
+constexpr int ROUTER_MODE = MONO_ROUTER_MODE;
+constexpr int N_GROUP = 8;
+constexpr int TOPK_GROUP = 4;
+constexpr int NK = K_DIM / 128;    // K slabs of the up projection
+constexpr int NP = N_HALF / 128;   // 128-column passes of the up projection = K slabs of the down projection
+constexpr int NHB = H_DIM / 256;   // 256-column passes of the down projection
+constexpr int TILE_M = 128;
+constexpr float BF16_MAX = 3.38953139e38f;
+
+static_assert(E == 256, "routing keeps 8 logits per lane: exactly 256 experts");
+static_assert(E_LOCAL > 0 && E_LOCAL <= E, "local experts are a subset");
+static_assert(K_DIM % 128 == 0 && N_HALF % 128 == 0 && H_DIM % 256 == 0, "geometry must tile by 128/256");
+static_assert(ROUTER_MODE >= 0 && ROUTER_MODE <= 2, "unknown router mode");
+static_assert(NK % 2 == 0, "activation quantisation pairs two 128-column groups per warp");
+static_assert(ROUTER_MODE != 2 || N_GROUP * 32 == E, "grouped routing assumes 32 experts per group");
+
+// ------------------------------------------------------------------ launch shape
+constexpr int BLOCK = 384;
+constexpr int NWARPS = BLOCK / 32;
+constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_GATHER0 = 2;  // warps 2,3 gather; warps 4..11 epilogue
+constexpr int N_GATHER = 64;
+constexpr int N_EPI = 256;
+constexpr int MAX_MY_TILES = 32;
+constexpr int MAX_TILES = MAX_MY_TILES * kGrid;
+
+// ------------------------------------------------------------------ shared memory plan
+constexpr int A_STAGE_BYTES = TILE_M * 128;  // 128 rows x 128 B
+constexpr int B_STAGE_BYTES = 256 * 128;     // 256 weight rows x 128 B
+constexpr int INTER_BYTES = NP * A_STAGE_BYTES;
+constexpr int SMEM_CAP = 227 * 1024;
+constexpr int SMEM_STATIC_RESERVE = 8 * 1024;
+constexpr int SMEM_AVAIL = SMEM_CAP - SMEM_STATIC_RESERVE - 1024 - INTER_BYTES;
+constexpr int SB_RAW = SMEM_AVAIL / (A_STAGE_BYTES + B_STAGE_BYTES);
+constexpr int SB = SB_RAW > 4 ? 4 : SB_RAW;
+constexpr int SA_RAW = (SMEM_AVAIL - SB * B_STAGE_BYTES) / A_STAGE_BYTES;
+constexpr int SA = SA_RAW > 4 ? 4 : SA_RAW;
+static_assert(SB >= 2 && SA >= 2, "intermediate too wide for shared memory: shard N_HALF further");
+constexpr int DYN_SMEM = 1024 + INTER_BYTES + SA * A_STAGE_BYTES + SB * B_STAGE_BYTES;
+static_assert(NWARPS * E * 4 <= SA * A_STAGE_BYTES + SB * B_STAGE_BYTES, "phase-0 histograms fit in the rings");
+
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t IDESC = umma_idesc_e4m3_f32(128, 256);
+
+// wait sites reported in the status word
+enum Site : uint32_t {
+  kSiteEmptyB = 1, kSiteFullB, kSiteFullA, kSiteEmptyA, kSiteTmemEmpty, kSiteTmemFull, kSiteInterReady,
+};
+
+struct Params {
+  const float* logits;
+  int num_tokens;
+  Workspace* ws;
+  int32_t* topk_ids;
+  float* topk_weights;
+  int32_t* sorted_ids;
+  const __nv_bfloat16* act_bf16;
+  uint8_t* act_fp8;
+  float* act_scales;
+  const float* up_w_scales;
+  const float* down_w_scales;
+  __nv_bfloat16* partial;   // [T*8, H] bf16 partial rows (the caller's output_accum buffer)
+  __nv_bfloat16* out;       // [T, H]
+  const float* router_bias;
+  const int32_t* expert_map;
+  // tensor-parallel epilogue
+  __nv_bfloat16* tp_mc;
+  uint32_t** tp_pads;
+  int tp_rank, tp_world, tp_nchunk, tp_ncomm;
+  uint32_t tp_seq;
+  uint32_t* tp_seqctr;
+  const __nv_bfloat16* residual;
+  float out_scale;
+  uint64_t timeout_ns;
+  // optional debug dump (null in production): raw gate|up accumulators, e4m3 intermediate, its scales
+  float* dbg_acc;
+  uint8_t* dbg_inter;
+  float* dbg_inter_scale;
+  alignas(64) CUtensorMap tm_up;
+  alignas(64) CUtensorMap tm_down;
+};
+
+struct TileInfo {
+  int e, row0, rows, pad;
+};
+
+// ------------------------------------------------------------------ small helpers
+__device__ __forceinline__ uint32_t float_key(float f) {
+  // Monotone map float -> uint32 for finite values; 0 is reserved for "not selectable".
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long k) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const unsigned long long o = __shfl_xor_sync(0xFFFFFFFFu, k, off);
+    k = o > k ? o : k;
+  }
+  return k;
+}
+__device__ __forceinline__ float warp_max_f(float v) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
+  return v;
+}
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+  return v;
+}
+// Byte offset of 16-byte chunk c of row r inside a [rows x 128 B] tile in the 128-byte
+// swizzle: eight-row groups of 1024 B, chunk position XORed with the row's low 3 bits.
+__device__ __forceinline__ uint32_t sw128(int r, int c) {
+  return static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
+}
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+// ------------------------------------------------------------------ phase 0: routing
+// One warp per token. Lane l holds experts l, l+32, ..., l+224; register slot j therefore
+// spans experts [32j, 32j+32), which is one DeepSeek expert group.
+// Semantics follow kernel/qwen_tp/src/prefill_mono_final_nb.cu:1025-1185: selection in
+// descending score order, ties to the lower expert id, weights renormalised by their sum
+// (clamped at 1e-30); modes 1/2 select on sigmoid+bias and weight by the unbiased sigmoid.
+// A slot for which no selectable expert remains gets id -1 and weight 0.
+__device__ __forceinline__ void route_token(const float* __restrict__ row, const float* __restrict__ bias,
+                                            int lane, int& my_id, float& my_w) {
+  float sel[8], unb[8];
+  float m = 0.f, s = 1.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sel[j] = row[lane + 32 * j];
+  if constexpr (ROUTER_MODE == 0) {
+    m = sel[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) m = fmaxf(m, sel[j]);
+    m = warp_max_f(m);
+    float part = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) part += det_expf(sel[j] - m);
+    s = warp_sum_f(part);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) unb[j] = sel[j];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = det_sigmoidf(sel[j]);
+      unb[j] = sg;
+      sel[j] = (bias != nullptr) ? __fadd_rn(sg, bias[lane + 32 * j]) : sg;
+    }
+    if constexpr (ROUTER_MODE == 2) {
+      float gs[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        // top-1 (with its lane, ties to the lower lane) and top-2 of the group
+        const bool ok = sel[j] > -FLT_MAX;
+        unsigned long long k1 = ok ? ((static_cast<unsigned long long>(float_key(sel[j])) << 32) |
+                                      static_cast<unsigned long long>(31 - lane))
+                                   : 0ull;
+        k1 = warp_max_u64(k1);
+        const int l1 = 31 - static_cast<int>(k1 & 0xFFFFFFFFull);
+        const float b1 = __shfl_sync(0xFFFFFFFFu, sel[j], l1 & 31);
+        float b2 = (lane == l1 || !ok) ? -FLT_MAX : sel[j];
+        b2 = warp_max_f(b2);
+        gs[j] = (k1 == 0ull) ? -FLT_MAX : __fadd_rn(b1, b2);
+      }
+      uint32_t keep = 0u;
+#pragma unroll
+      for (int r = 0; r < TOPK_GROUP; ++r) {
+        float gb = -FLT_MAX;
+        int gi = -1;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (!((keep >> j) & 1u) && gs[j] > gb) { gb = gs[j]; gi = j; }
+        if (gi >= 0) keep |= 1u << gi;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (!((keep >> j) & 1u)) sel[j] = -FLT_MAX;
+    }
+  }
+
+  uint32_t used = 0u;
+  float wsum = 0.f;
+  my_id = -1;
+  my_w = 0.f;
+#pragma unroll 1
+  for (int k = 0; k < TOP_K; ++k) {
+    unsigned long long best = 0ull;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      // `+ 0.0f` folds -0 into +0 so that the integer key orders exactly like operator>.
+      const float v = sel[j] + 0.0f;
+      const bool ok = !((used >> j) & 1u) && (v > -FLT_MAX);
+      const unsigned long long key =
+          ok ? ((static_cast<unsigned long long>(float_key(v)) << 32) |
+                static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<uint32_t>(lane + 32 * j)))
+             : 0ull;
+      best = key > best ? key : best;
+    }
+    best = warp_max_u64(best);
+    int bidx = -1;
+    float wk = 0.f;
+    if (best != 0ull) {
+      bidx = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(best & 0xFFFFFFFFull));
+      const int owner = bidx & 31, slot = bidx >> 5;
+      float mine = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j == slot) mine = unb[j];
+      const float bu = __shfl_sync(0xFFFFFFFFu, mine, owner);
+      if (lane == owner) used |= 1u << slot;
+      wk = (ROUTER_MODE == 0) ? __fdiv_rn(det_expf(bu - m), s) : bu;
+    }
+    wsum += wk;
+    if (lane == k) { my_id = bidx; my_w = wk; }
+  }
+  const float inv = __fdiv_rn(1.0f, fmaxf(wsum, 1e-30f));
+  my_w = __fmul_rn(my_w, inv);
+}
+
+// ------------------------------------------------------------------ phase 0.5: activation quantisation
+// bf16 -> e4m3 with one fp32 scale per (token, 128 columns): amax, inv = 448/amax,
+// q = e4m3_rn_satfinite(x * inv), scale = amax/448; amax < FLT_MIN is treated as 1
+// (kernel/qwen_tp/src/prefill_mono_final_nb.cu:1225-1244). A half-warp owns one group.
+__device__ __forceinline__ void quantize_activations(const Params& p, int gwarp, int nwarps, int lane) {
+  const long long ngroups = static_cast<long long>(p.num_tokens) * NK;
+  const int half = lane >> 4, sub = lane & 15;
+  constexpr int U = 4;
+  for (long long g0 = static_cast<long long>(gwarp) * 2 + half; g0 < ngroups;
+       g0 += static_cast<long long>(nwarps) * 2 * U) {
+    uint4 raw[U];
+    bool live[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long g = g0 + static_cast<long long>(nwarps) * 2 * u;
+      live[u] = g < ngroups;
+      raw[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (live[u]) {
+        const long long tok = g / NK;
+        const int kb = static_cast<int>(g % NK);
+        raw[u] = *reinterpret_cast<const uint4*>(p.act_bf16 + tok * K_DIM + kb * 128 + sub * 8);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long g = g0 + static_cast<long long>(nwarps) * 2 * u;
+      const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&raw[u]);
+      float x[8];
+      float am = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        x[i] = __bfloat162float(b[i]);
+        am = fmaxf(am, fabsf(x[i]));
+      }
+      // reduce inside the 16-lane half (all 32 lanes execute the shuffles)
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, off));
+      if (am < FLT_MIN) am = 1.f;
+      const float inv = __fdiv_rn(448.0f, am);
+      if (live[u]) {
+        const long long tok = g / NK;
+        const int kb = static_cast<int>(g % NK);
+        uint2 q;
+        q.x = pack_e4m3x4(__fmul_rn(x[0], inv), __fmul_rn(x[1], inv), __fmul_rn(x[2], inv), __fmul_rn(x[3], inv));
+        q.y = pack_e4m3x4(__fmul_rn(x[4], inv), __fmul_rn(x[5], inv), __fmul_rn(x[6], inv), __fmul_rn(x[7], inv));
+        *reinterpret_cast<uint2*>(p.act_fp8 + tok * K_DIM + kb * 128 + sub * 8) = q;
+        if (sub == 0) p.act_scales[tok * NK + kb] = __fdiv_rn(am, 448.0f);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ shared state
+struct __align__(16) SharedState {
+  uint64_t fullA[4], emptyA[4], fullB[4], emptyB[4];
+  uint64_t tmem_full[2], tmem_empty[2];
+  uint64_t inter_ready;
+  uint32_t tmem_base;
+  uint32_t flag;          // grid_sync result broadcast
+  int n_my_tiles;
+  int total_tiles;
+  TileInfo tiles[MAX_MY_TILES];
+  int scan_cnt[E];
+  int scan_tile[E];
+  int tot[E];
+  int pre[E];
+  float rowmax[2][2][TILE_M];
+};
+static_assert(sizeof(SharedState) <= SMEM_STATIC_RESERVE, "static shared state exceeds its reserve");
+
+// ------------------------------------------------------------------ the kernel
+__global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_constant__ Params p) {
+  extern __shared__ uint8_t dyn_raw[];
+  __shared__ SharedState S;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bid = blockIdx.x;
+  const WaitCtx wc{p.ws, p.timeout_ns};
+  Workspace* ws = p.ws;
+  const int T = p.num_tokens;
+  const int numel = T * TOP_K;
+
+  // 1024-byte aligned base of the operand buffers
+  const uint32_t dyn_u32 = (smem_u32(dyn_raw) + 1023u) & ~1023u;
+  uint8_t* dyn = dyn_raw + (dyn_u32 - smem_u32(dyn_raw));
+  uint8_t* inter = dyn;
+  uint8_t* a_ring = dyn + INTER_BYTES;
+  uint8_t* b_ring = a_ring + SA * A_STAGE_BYTES;
+  int* hist = reinterpret_cast<int*>(a_ring);  // [NWARPS][E], phases 0-1 only
+
+  if (bid == 0 && tid == 0) ws->phase_ns[0] = globaltimer_ns();
+
+  // launch sequence of the tensor-parallel epilogue: a device counter outside the
+  // workspace (which is zeroed every launch) so that CUDA-graph replays advance it
+  // (kernel/qwen_tp/src/prefill_mono_final_nb.cu:985-1016)
+  const bool tp_on = (p.tp_mc != nullptr) && (p.tp_pads != nullptr) && (p.tp_ncomm > 0);
+  if (tp_on && p.tp_seqctr != nullptr && bid == 0 && tid == 0) {
+    const uint32_t sq = atomicAdd(p.tp_seqctr, 1u) + 1u;
+    atomicExch(&ws->tp_seq_pub, sq);
+  }
+
+  // ================================================================ phase 0
+  for (int i = tid; i < NWARPS * E; i += BLOCK) hist[i] = 0;
+  __syncthreads();
+
+  const int gwarp = bid * NWARPS + warp;
+  const int nwarps_grid = kGrid * NWARPS;
+  const int tok_per_warp = (T + nwarps_grid - 1) / nwarps_grid;
+  const int t_begin = min(T, gwarp * tok_per_warp);
+  const int t_end = min(T, t_begin + tok_per_warp);
+
+  for (int t = t_begin; t < t_end; ++t) {
+    int my_id;
+    float my_w;
+    route_token(p.logits + static_cast<size_t>(t) * E, p.router_bias, lane, my_id, my_w);
+    if (lane < TOP_K) {
+      int lid = my_id;
+      if constexpr (EP_BUILD) lid = (my_id >= 0) ? p.expert_map[my_id] : -1;
+      if (lid >= E_LOCAL) lid = -1;
+      p.topk_ids[t * TOP_K + lane] = lid;
+      p.topk_weights[t * TOP_K + lane] = my_w;
+      if (lid >= 0) hist[warp * E + lid] += 1;  // ids of one token are distinct: no conflict
+    }
+    __syncwarp();
+  }
+  quantize_activations(p, gwarp, nwarps_grid, lane);
+  __syncthreads();
+  if (tid < E) {
+    int c = 0;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) c += hist[w * E + tid];
+    ws->cta_hist[bid][tid] = c;
+  }
+
+  bool alive = grid_sync(wc, 0, &S.flag);
+  if (bid == 0 && tid == 0) ws->phase_ns[1] = globaltimer_ns();
+
+  // ================================================================ phase 1
+  if (alive) {
+    if (tid < E) { S.tot[tid] = 0; S.pre[tid] = 0; }
+    __syncthreads();
+    {
+      // 64 column groups of 4 experts x 6 row groups of CTAs
+      const int col = tid & 63, rg = tid >> 6;
+      int4 tot = make_int4(0, 0, 0, 0), pre = make_int4(0, 0, 0, 0);
+#pragma unroll 5
+      for (int b = rg; b < kGrid; b += 6) {
+        const int4 c = __ldcg(reinterpret_cast<const int4*>(&ws->cta_hist[b][col * 4]));
+        tot.x += c.x; tot.y += c.y; tot.z += c.z; tot.w += c.w;
+        if (b < bid) { pre.x += c.x; pre.y += c.y; pre.z += c.z; pre.w += c.w; }
+      }
+      atomicAdd(&S.tot[col * 4 + 0], tot.x); atomicAdd(&S.tot[col * 4 + 1], tot.y);
+      atomicAdd(&S.tot[col * 4 + 2], tot.z); atomicAdd(&S.tot[col * 4 + 3], tot.w);
+      atomicAdd(&S.pre[col * 4 + 0], pre.x); atomicAdd(&S.pre[col * 4 + 1], pre.y);
+      atomicAdd(&S.pre[col * 4 + 2], pre.z); atomicAdd(&S.pre[col * 4 + 3], pre.w);
+    }
+    __syncthreads();
+    int cnt = 0, tiles_e = 0;
+    if (tid < E) {
+      cnt = S.tot[tid];
+      tiles_e = (cnt + TILE_M - 1) / TILE_M;
+      S.scan_cnt[tid] = cnt;
+      S.scan_tile[tid] = tiles_e;
+    }
+    __syncthreads();
+    for (int d = 1; d < E; d <<= 1) {
+      int vc = 0, vt = 0;
+      if (tid < E && tid >= d) { vc = S.scan_cnt[tid - d]; vt = S.scan_tile[tid - d]; }
+      __syncthreads();
+      if (tid < E) { S.scan_cnt[tid] += vc; S.scan_tile[tid] += vt; }
+      __syncthreads();
+    }
+    if (tid < E) {
+      const int off_e = S.scan_cnt[tid] - cnt;
+      const int tbase = S.scan_tile[tid] - tiles_e;
+      if (tid == E - 1) S.total_tiles = tbase + tiles_e;
+      if (bid == 0) {
+        ws->expert_counts[tid] = cnt;
+        ws->expert_offsets[tid] = off_e;
+        if (tid == E - 1) {
+          ws->expert_offsets[E] = off_e + cnt;
+          ws->total_tiles = tbase + tiles_e;
+        }
+      }
+      for (int i = 0; i < tiles_e; ++i) {
+        const int g = tbase + i;
+        if (g % kGrid == bid) {
+          const int slot = g / kGrid;
+          if (slot < MAX_MY_TILES) {
+            TileInfo ti;
+            ti.e = tid;
+            ti.row0 = off_e + i * TILE_M;
+            ti.rows = min(TILE_M, off_e + cnt - ti.row0);
+            ti.pad = 0;
+            S.tiles[slot] = ti;
+          } else {
+            report_error(ws, kErrBounds, 1, static_cast<uint32_t>(g), static_cast<uint32_t>(slot));
+          }
+        }
+      }
+      // turn the per-warp histograms into per-warp write cursors
+      int base = off_e + S.pre[tid];
+#pragma unroll
+      for (int w = 0; w < NWARPS; ++w) {
+        const int h = hist[w * E + tid];
+        hist[w * E + tid] = base;
+        base += h;
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      const int tt = S.total_tiles;
+      S.n_my_tiles = (tt > bid) ? min(MAX_MY_TILES, (tt - bid + kGrid - 1) / kGrid) : 0;
+    }
+    // stable scatter: each warp re-walks its own tokens in ascending order
+    for (int t = t_begin; t < t_end; ++t) {
+      if (lane < TOP_K) {
+        const int lid = p.topk_ids[t * TOP_K + lane];
+        if (lid >= 0) {
+          const int pos = hist[warp * E + lid]++;
+          if (pos >= 0 && pos < numel) p.sorted_ids[pos] = t * TOP_K + lane;
+          else report_error(ws, kErrBounds, 2, static_cast<uint32_t>(pos), static_cast<uint32_t>(t));
+        }
+      }
+      __syncwarp();
+    }
+  }
+
+  alive = grid_sync(wc, 1, &S.flag) && alive;
+  if (bid == 0 && tid == 0) ws->phase_ns[2] = globaltimer_ns();
+
+  // ================================================================ phase 2
+  if (tid == 0) {
+    for (int s = 0; s < SA; ++s) { mbar_init(&S.fullA[s], N_GATHER); mbar_init(&S.emptyA[s], 1); }
+    for (int s = 0; s < SB; ++s) { mbar_init(&S.fullB[s], 1); mbar_init(&S.emptyB[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&S.tmem_full[s], 1); mbar_init(&S.tmem_empty[s], N_EPI); }
+    mbar_init(&S.inter_ready, N_EPI);
+    mbar_init_fence();
+  }
+  if (warp == WARP_MMA) {
+    tmem_alloc(&S.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = S.tmem_base;
+  const int n_my = alive ? S.n_my_tiles : 0;
+
+  if (warp < 4) {
+    if (warp == WARP_TMA) {
+      // ---------------------------------------------------------- weight producer
+      if (lane == 0) {
+        tma_prefetch_desc(&p.tm_up);
+        tma_prefetch_desc(&p.tm_down);
+        uint32_t nb = 0;
+        bool ok = true;
+        for (int it = 0; it < n_my && ok; ++it) {
+          const int e = S.tiles[it].e;
+          for (int ps = 0; ps < NP && ok; ++ps) {
+            const uint32_t yg = static_cast<uint32_t>(e * N_UP + ps * 128);
+            const uint32_t yu = yg + N_HALF;
+            for (int ks = 0; ks < NK; ++ks) {
+              const uint32_t st = nb % SB, ph = (nb / SB) & 1u;
+              if (!mbar_wait(&S.emptyB[st], ph ^ 1u, wc, kSiteEmptyB)) { ok = false; break; }
+              mbar_arrive_expect_tx(&S.fullB[st], B_STAGE_BYTES);
+              uint8_t* dst = b_ring + st * B_STAGE_BYTES;
+              const uint32_t x = static_cast<uint32_t>(ks * 128);
+              // shared rows [0,64) gate c..c+63 | [64,128) up c..c+63 | [128,192) gate c+64.. | [192,256) up c+64..
+              tma_load_2d(&p.tm_up, x, yg, dst, &S.fullB[st]);
+              tma_load_2d(&p.tm_up, x, yu, dst + 8192, &S.fullB[st]);
+              tma_load_2d(&p.tm_up, x, yg + 64, dst + 16384, &S.fullB[st]);
+              tma_load_2d(&p.tm_up, x, yu + 64, dst + 24576, &S.fullB[st]);
+              ++nb;
+            }
+          }
+          for (int hb = 0; hb < NHB && ok; ++hb) {
+            const uint32_t y = static_cast<uint32_t>(e * H_DIM + hb * 256);
+            for (int dk = 0; dk < NP; ++dk) {
+              const uint32_t st = nb % SB, ph = (nb / SB) & 1u;
+              if (!mbar_wait(&S.emptyB[st], ph ^ 1u, wc, kSiteEmptyB)) { ok = false; break; }
+              mbar_arrive_expect_tx(&S.fullB[st], B_STAGE_BYTES);
+              uint8_t* dst = b_ring + st * B_STAGE_BYTES;
+              const uint32_t x = static_cast<uint32_t>(dk * 128);
+              tma_load_2d(&p.tm_down, x, y, dst, &S.fullB[st]);
+              tma_load_2d(&p.tm_down, x, y + 64, dst + 8192, &S.fullB[st]);
+              tma_load_2d(&p.tm_down, x, y + 128, dst + 16384, &S.fullB[st]);
+              tma_load_2d(&p.tm_down, x, y + 192, dst + 24576, &S.fullB[st]);
+              ++nb;
+            }
+          }
+        }
+      }
+    } else if (warp == WARP_MMA) {
+      // ---------------------------------------------------------- MMA issuer
+      if (lane == 0) {
+        uint32_t nb = 0, na = 0, nt = 0;
+        bool ok = true;
+        const uint32_t a_ring_u32 = smem_u32(a_ring), b_ring_u32 = smem_u32(b_ring), inter_u32 = smem_u32(inter);
+        for (int it = 0; it < n_my && ok; ++it) {
+          for (int s = 0; s < NP * NK; ++s) {
+            const uint32_t sb = nb % SB, sa = na % SA, buf = nt & 1u;
+            if (!mbar_wait(&S.fullB[sb], (nb / SB) & 1u, wc, kSiteFullB)) { ok = false; break; }
+            if (!mbar_wait(&S.fullA[sa], (na / SA) & 1u, wc, kSiteFullA)) { ok = false; break; }
+            if (!mbar_wait(&S.tmem_empty[buf], ((nt >> 1) & 1u) ^ 1u, wc, kSiteTmemEmpty)) { ok = false; break; }
+            tc_fence_after();
+            const uint64_t da = umma_desc_sw128(a_ring_u32 + sa * A_STAGE_BYTES);
+            const uint64_t db = umma_desc_sw128(b_ring_u32 + sb * B_STAGE_BYTES);
+            const uint32_t d = tmem_base + buf * 256u;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+            umma_commit(&S.emptyA[sa]);
+            umma_commit(&S.emptyB[sb]);
+            umma_commit(&S.tmem_full[buf]);
+            ++nb; ++na; ++nt;
+          }
+          if (!ok) break;
+          if (!mbar_wait(&S.inter_ready, static_cast<uint32_t>(it) & 1u, wc, kSiteInterReady)) { ok = false; break; }
+          tc_fence_after();
+          for (int s = 0; s < NHB * NP; ++s) {
+            const int dk = s % NP;
+            const uint32_t sb = nb % SB, buf = nt & 1u;
+            if (!mbar_wait(&S.fullB[sb], (nb / SB) & 1u, wc, kSiteFullB)) { ok = false; break; }
+            if (!mbar_wait(&S.tmem_empty[buf], ((nt >> 1) & 1u) ^ 1u, wc, kSiteTmemEmpty)) { ok = false; break; }
+            tc_fence_after();
+            const uint64_t da = umma_desc_sw128(inter_u32 + dk * A_STAGE_BYTES);
+            const uint64_t db = umma_desc_sw128(b_ring_u32 + sb * B_STAGE_BYTES);
+            const uint32_t d = tmem_base + buf * 256u;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+            umma_commit(&S.emptyB[sb]);
+            umma_commit(&S.tmem_full[buf]);
+            ++nb; ++nt;
+          }
+        }
+      }
+    } else {
+      // ---------------------------------------------------------- activation gather (64 threads)
+      const int gt = tid - WARP_GATHER0 * 32;
+      uint32_t na = 0;
+      bool ok = true;
+      const uint32_t a_ring_u32 = smem_u32(a_ring);
+      for (int it = 0; it < n_my && ok; ++it) {
+        const TileInfo ti = S.tiles[it];
+        const uint8_t* src[2];
+        uint32_t off[2][8];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int r = gt + h * 64;
+          src[h] = nullptr;
+          if (r < ti.rows) {
+            const int fi = __ldcg(&p.sorted_ids[ti.row0 + r]);
+            if (fi >= 0 && fi < numel) src[h] = p.act_fp8 + static_cast<size_t>(fi / TOP_K) * K_DIM;
+          }
+#pragma unroll
+          for (int c = 0; c < 8; ++c) off[h][c] = sw128(r, c);
+        }
+        int prev = -1;
+        for (int s = 0; s < NP * NK; ++s) {
+          const int ks = s % NK;
+          const uint32_t sa = na % SA;
+          if (!mbar_wait(&S.emptyA[sa], ((na / SA) & 1u) ^ 1u, wc, kSiteEmptyA)) { ok = false; break; }
+          const uint32_t dst = a_ring_u32 + sa * A_STAGE_BYTES;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (src[h] != nullptr) {
+              const uint8_t* g = src[h] + ks * 128;
+#pragma unroll
+              for (int c = 0; c < 8; ++c) cp_async16(dst + off[h][c], g + c * 16);
+            }
+          }
+          cp_async_commit();
+          if (prev >= 0) {
+            cp_async_wait<1>();
+            fence_proxy_async_smem();
+            mbar_arrive(&S.fullA[prev]);
+          }
+          prev = static_cast<int>(sa);
+          ++na;
+        }
+        cp_async_wait<0>();
+        if (ok && prev >= 0) {
+          fence_proxy_async_smem();
+          mbar_arrive(&S.fullA[prev]);
+        }
+      }
+      cp_async_wait<0>();
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue (256 threads)
+    {
+      const int et = tid - 128;
+      const int h = et >> 7;               // which 128 TMEM columns of the 256-column buffer
+      const int q = warp & 3;              // TMEM lane quarter this warp may read
+      const int r = q * 32 + lane;         // row of the tile
+      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(h * 128);
+      uint32_t nt = 0;
+      bool dead = false;  // after an abort: keep the loop structure (named barriers stay matched), skip the work
+      float acc[128];
+
+      for (int it = 0; it < n_my; ++it) {
+        const TileInfo ti = S.tiles[it];
+        const int e = ti.e;
+        int fi = -1;
+        if (r < ti.rows) {
+          fi = __ldcg(&p.sorted_ids[ti.row0 + r]);
+          if (fi < 0 || fi >= numel) fi = -1;
+        }
+        const float rw = (fi >= 0) ? __ldcg(&p.topk_weights[fi]) : 0.f;
+        const float* as_row = (fi >= 0) ? (p.act_scales + static_cast<size_t>(fi / TOP_K) * NK) : nullptr;
+        float iscale[NP];
+
+        // ---------------- up projection + SiLU*mul + requantisation
+        for (int ps = 0; ps < NP; ++ps) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+          const float* wsg_p = p.up_w_scales + (static_cast<size_t>(e) * (2 * NP) + ps) * NK;
+          const float* wsu_p = wsg_p + static_cast<size_t>(NP) * NK;
+          float as_n = as_row ? __ldcg(as_row) : 0.f;
+          float wg_n = __ldg(wsg_p), wu_n = __ldg(wsu_p);
+          for (int ks = 0; ks < NK; ++ks) {
+            const float a_s = as_n, w_g = wg_n, w_u = wu_n;
+            if (ks + 1 < NK) {
+              as_n = as_row ? __ldcg(as_row + ks + 1) : 0.f;
+              wg_n = __ldg(wsg_p + ks + 1);
+              wu_n = __ldg(wsu_p + ks + 1);
+            }
+            const uint32_t buf = nt & 1u;
+            if (!dead && !mbar_wait(&S.tmem_full[buf], (nt >> 1) & 1u, wc, kSiteTmemFull)) dead = true;
+            if (!dead) {
+              tc_fence_after();
+              const float sg = __fmul_rn(w_g, a_s), su = __fmul_rn(w_u, a_s);
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tmem_ld32(t_lane + buf * 256u + c * 32u, v);
+                tmem_ld_wait();
+                const float sc = (c < 2) ? sg : su;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __fmaf_rn(__uint_as_float(v[j]), sc, acc[c * 32 + j]);
+              }
+              tc_fence_before();
+              mbar_arrive(&S.tmem_empty[buf]);
+            }
+            ++nt;
+          }
+          if (p.dbg_acc != nullptr && fi >= 0 && !dead) {
+            float* d = p.dbg_acc + static_cast<size_t>(ti.row0 + r) * N_UP;
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+              d[ps * 128 + h * 64 + j] = acc[j];
+              d[N_HALF + ps * 128 + h * 64 + j] = acc[64 + j];
+            }
+          }
+          // SiLU(gate) * up, written over the gate half of the accumulators
+          float mx = 0.f;
+#pragma unroll
+          for (int j = 0; j < 64; ++j) {
+            const float g = acc[j];
+            const float v = __fdividef(acc[64 + j] * g, 1.0f + __expf(-g));
+            acc[j] = v;
+            mx = fmaxf(mx, fabsf(v));
+          }
+          S.rowmax[ps & 1][h][r] = mx;
+          named_bar_sync(1, N_EPI);
+          mx = fmaxf(mx, S.rowmax[ps & 1][h ^ 1][r]);
+          const bool nz = mx > FLT_MIN;
+          const float inv = nz ? __fdiv_rn(448.0f, mx) : 0.f;
+          const float my_scale = nz ? __fdiv_rn(mx, 448.0f) : (1.0f / 448.0f);
+#pragma unroll
+          for (int qq = 0; qq < NP; ++qq)
+            if (qq == ps) iscale[qq] = my_scale;  // static indexing keeps the array in registers
+          uint8_t* irow = inter + ps * A_STAGE_BYTES;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint4 qv;
+            qv.x = pack_e4m3x4(acc[c * 16 + 0] * inv, acc[c * 16 + 1] * inv, acc[c * 16 + 2] * inv, acc[c * 16 + 3] * inv);
+            qv.y = pack_e4m3x4(acc[c * 16 + 4] * inv, acc[c * 16 + 5] * inv, acc[c * 16 + 6] * inv, acc[c * 16 + 7] * inv);
+            qv.z = pack_e4m3x4(acc[c * 16 + 8] * inv, acc[c * 16 + 9] * inv, acc[c * 16 + 10] * inv, acc[c * 16 + 11] * inv);
+            qv.w = pack_e4m3x4(acc[c * 16 + 12] * inv, acc[c * 16 + 13] * inv, acc[c * 16 + 14] * inv, acc[c * 16 + 15] * inv);
+            *reinterpret_cast<uint4*>(irow + sw128(r, h * 4 + c)) = qv;
+            if (p.dbg_inter != nullptr && fi >= 0 && !dead)
+              *reinterpret_cast<uint4*>(p.dbg_inter + static_cast<size_t>(ti.row0 + r) * N_HALF + ps * 128 + h * 64 + c * 16) = qv;
+          }
+          if (p.dbg_inter_scale != nullptr && fi >= 0 && h == 0 && !dead)
+            p.dbg_inter_scale[static_cast<size_t>(ti.row0 + r) * NP + ps] = my_scale;
+        }
+        // publish the intermediate to the tensor core (async proxy) and release the MMA thread
+        fence_proxy_async_smem();
+        mbar_arrive(&S.inter_ready);
+
+        // ---------------- down projection, routing weight, bf16 partial rows
+        for (int hb = 0; hb < NHB; ++hb) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+          const float* dws_p = p.down_w_scales + (static_cast<size_t>(e) * (H_DIM / 128) + hb * 2 + h) * NP;
+#pragma unroll
+          for (int dk = 0; dk < NP; ++dk) {
+            const float sc = __fmul_rn(__ldg(dws_p + dk), iscale[dk]);
+            const uint32_t buf = nt & 1u;
+            if (!dead && !mbar_wait(&S.tmem_full[buf], (nt >> 1) & 1u, wc, kSiteTmemFull)) dead = true;
+            if (!dead) {
+              tc_fence_after();
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tmem_ld32(t_lane + buf * 256u + c * 32u, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __fmaf_rn(__uint_as_float(v[j]), sc, acc[c * 32 + j]);
+              }
+              tc_fence_before();
+              mbar_arrive(&S.tmem_empty[buf]);
+            }
+            ++nt;
+          }
+          if (fi >= 0 && !dead) {
+            __nv_bfloat16* dst = p.partial + static_cast<size_t>(fi) * H_DIM + hb * 256 + h * 128;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float v0 = acc[c * 8 + 2 * j] * rw, v1 = acc[c * 8 + 2 * j + 1] * rw;
+                v0 = fminf(fmaxf(v0, -BF16_MAX), BF16_MAX);
+                v1 = fminf(fmaxf(v1, -BF16_MAX), BF16_MAX);
+                const __nv_bfloat162 b2 = __floats2bfloat162_rn(v0, v1);
+                w[j] = *reinterpret_cast<const uint32_t*>(&b2);
+              }
+              *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // teardown of phase 2: when aborting, give in-flight bulk copies and MMAs time to land
+  if (aborted(ws)) __nanosleep(200000);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == WARP_MMA) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+
+  alive = grid_sync(wc, 2, &S.flag) && alive;
+  if (bid == 0 && tid == 0) ws->phase_ns[3] = globaltimer_ns();
+  if (!alive) return;
+
+  // ================================================================ phase 3
+  // out[t,:] = bf16( sum_k partial[t*8+k,:] * out_scale (+ residual[t,:]) ), k ascending, fp32
+  // (kernel/qwen_tp/src/prefill_mono_final_nb.cu:1377-1460). Under expert parallelism slots
+  // this rank does not own were never written and are skipped (kernel/qwen_ep/...:1459-1481).
+  {
+    constexpr int W = 8;                    // bf16 per 16-byte vector
+    constexpr int HV = H_DIM / W;
+    const size_t out_vec = static_cast<size_t>(T) * HV;
+    const int ncomp = tp_on ? (kGrid - p.tp_ncomm) : kGrid;
+    const int nchunk = tp_on ? p.tp_nchunk : 1;
+    const uint32_t seq = (p.tp_seqctr != nullptr) ? ld_relaxed_gpu(&ws->tp_seq_pub) : p.tp_seq;
+
+    if (!tp_on || bid < ncomp) {
+      const size_t stride = static_cast<size_t>(ncomp) * BLOCK;
+      for (int c = 0; c < nchunk; ++c) {
+        const size_t c_lo = out_vec * c / nchunk, c_hi = out_vec * (c + 1) / nchunk;
+        for (size_t iv = c_lo + static_cast<size_t>(bid) * BLOCK + tid; iv < c_hi; iv += stride) {
+          const size_t tok = iv / HV;
+          const int hv = static_cast<int>(iv % HV);
+          int own[TOP_K];
+          if constexpr (EP_BUILD) {
+            const int4* o = reinterpret_cast<const int4*>(p.topk_ids + tok * TOP_K);
+            const int4 o0 = o[0], o1 = o[1];
+            own[0] = o0.x; own[1] = o0.y; own[2] = o0.z; own[3] = o0.w;
+            own[4] = o1.x; own[5] = o1.y; own[6] = o1.z; own[7] = o1.w;
+          }
+          float s[W];
+#pragma unroll
+          for (int i = 0; i < W; ++i) s[i] = 0.f;
+          uint4 raw[TOP_K];
+#pragma unroll
+          for (int k = 0; k < TOP_K; ++k) {
+            bool mine = true;
+            if constexpr (EP_BUILD) mine = own[k] >= 0;
+            raw[k] = make_uint4(0u, 0u, 0u, 0u);
+            if (mine)
+              raw[k] = __ldcg(reinterpret_cast<const uint4*>(p.partial + (tok * TOP_K + k) * H_DIM + hv * W));
+          }
+#pragma unroll
+          for (int k = 0; k < TOP_K; ++k) {
+            const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&raw[k]);
+#pragma unroll
+            for (int i = 0; i < W; ++i) s[i] += __bfloat162float(b[i]);
+          }
+          __nv_bfloat16 o[W];
+          if (p.residual != nullptr) {
+            const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + iv * W);
+            const __nv_bfloat16* rb = reinterpret_cast<const __nv_bfloat16*>(&rr);
+#pragma unroll
+            for (int i = 0; i < W; ++i) o[i] = __float2bfloat16(__fmaf_rn(s[i], p.out_scale, __bfloat162float(rb[i])));
+          } else {
+#pragma unroll
+            for (int i = 0; i < W; ++i) o[i] = __float2bfloat16(__fmul_rn(s[i], p.out_scale));
+          }
+          *reinterpret_cast<uint4*>(p.out + iv * W) = *reinterpret_cast<const uint4*>(o);
+        }
+        if (!tp_on) continue;
+        __threadfence_system();  // a peer's communication block reads these bytes through the multicast alias
+        __syncthreads();
+        if (tid == 0) atomicAdd(&ws->tp_ready[c], 1u);
+      }
+    } else {
+      // ---------------------------------------------------------- communication blocks
+      // Chunked one-shot all-reduce (kernel/qwen_tp/src/prefill_mono_final_nb.cu:1461-1504):
+      // chunk c is split over world*ncomm shards aligned to 512 B; each shard is summed
+      // across ranks by multimem.ld_reduce and written back to every rank by multimem.st.
+      const int cb = bid - ncomp;
+      const int nsh = p.tp_world * p.tp_ncomm;
+      const int sh = p.tp_rank * p.tp_ncomm + cb;
+      const size_t out_mv = static_cast<size_t>(T) * H_DIM / 8;
+      constexpr size_t ALIGN = 32;
+      bool ok = true;
+      auto rank_barrier = [&](int slot) -> bool {
+        // arrive on every peer's window, then wait for every peer on mine
+        for (int rk = 0; rk < p.tp_world; ++rk)
+          st_release_sys(p.tp_pads[rk] + static_cast<size_t>(slot) * p.tp_world + p.tp_rank, seq);
+        for (int rk = 0; rk < p.tp_world; ++rk) {
+          const uint32_t* w = p.tp_pads[p.tp_rank] + static_cast<size_t>(slot) * p.tp_world + rk;
+          const uint64_t t0 = globaltimer_ns();
+          uint32_t polls = 0;
+          while (ld_acquire_sys(w) < seq) {
+            if ((++polls & 15u) == 0u) {
+              if (aborted(ws)) return false;
+              if (globaltimer_ns() - t0 > p.timeout_ns) {
+                report_error(ws, kErrRankBarrier, static_cast<uint32_t>(slot), static_cast<uint32_t>(rk), seq);
+                return false;
+              }
+            }
+          }
+        }
+        return true;
+      };
+      for (int c = 0; c < nchunk; ++c) {
+        if (tid == 0) {
+          ok = wait_counter_ge(&ws->tp_ready[c], static_cast<uint32_t>(ncomp), wc, kErrChunkReady, static_cast<uint32_t>(c));
+          if (ok) ok = rank_barrier(c * p.tp_ncomm + cb);
+          S.flag = ok ? 1u : 0u;
+        }
+        __syncthreads();
+        ok = S.flag != 0u;
+        __syncthreads();
+        if (!ok) break;
+        const size_t lo = out_mv * c / nchunk, hi = out_mv * (c + 1) / nchunk;
+        const size_t ng = (hi - lo + ALIGN - 1) / ALIGN;
+        size_t s_lo = lo + (ng * sh / nsh) * ALIGN, s_hi = lo + (ng * (sh + 1) / nsh) * ALIGN;
+        s_lo = s_lo < hi ? s_lo : hi;
+        s_hi = s_hi < hi ? s_hi : hi;
+        constexpr int UN = 4;
+        for (size_t base = s_lo + tid; base < s_hi; base += static_cast<size_t>(UN) * BLOCK) {
+          uint32_t x[UN][4];
+          bool live[UN];
+#pragma unroll
+          for (int u = 0; u < UN; ++u) {
+            const size_t v = base + static_cast<size_t>(u) * BLOCK;
+            live[u] = v < s_hi;
+            if (live[u]) multimem_ld_reduce_bf16x8(p.tp_mc + v * 8, x[u][0], x[u][1], x[u][2], x[u][3]);
+          }
+#pragma unroll
+          for (int u = 0; u < UN; ++u) {
+            const size_t v = base + static_cast<size_t>(u) * BLOCK;
+            if (live[u]) multimem_st_b128(p.tp_mc + v * 8, x[u][0], x[u][1], x[u][2], x[u][3]);
+          }
+        }
+      }
+      __threadfence_system();
+      __syncthreads();
+      if (tid == 0 && ok) {
+        if (atomicAdd(&ws->tp_done_local, 1u) == static_cast<uint32_t>(p.tp_ncomm) - 1u) {
+          if (rank_barrier(nchunk * p.tp_ncomm)) {
+            __threadfence();
+            atomicExch(&ws->tp_done_flag, 1u);
+          }
+        } else {
+          wait_counter_ge(&ws->tp_done_flag, 1u, wc, kErrDoneFlag, 0);
+        }
+      }
+      __syncthreads();
+    }
+  }
+  if (bid == 0 && tid == 0) ws->phase_ns[4] = globaltimer_ns();
+}
+
+// ------------------------------------------------------------------ host side
+uint64_t g_timeout_ns = 2000000000ull;  // bound of every device-side wait: 2 s
+float* g_dbg_acc = nullptr;
+uint8_t* g_dbg_inter = nullptr;
+float* g_dbg_inter_scale = nullptr;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is fetched through the runtime, so the library has no link-time
+// dependency on libcuda and its accessors load on a machine without a driver.
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// 2-D u8 tensor [rows, cols] row-major, box 64 rows x 128 bytes, 128-byte swizzle.
+int make_weight_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t gd[2] = {cols, rows};
+  cuuint64_t gs[1] = {cols};
+  cuuint32_t bx[2] = {128u, 64u};
+  cuuint32_t es[2] = {1u, 1u};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gd, gs, bx, es,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+}  // namespace
+}  // namespace mono
+
+using namespace mono;
+
+extern "C" {
+
+size_t prefill_wgmma_workspace_bytes() { return sizeof(Workspace); }
+int prefill_wgmma_num_experts() { return E; }
+int prefill_wgmma_num_experts_local() { return E_LOCAL; }
+int prefill_wgmma_ep_capable() { return EP_BUILD ? 1 : 0; }
+int prefill_wgmma_top_k() { return TOP_K; }
+int prefill_wgmma_max_tiles() { return MAX_TILES; }
+int prefill_wgmma_grid_size() { return kGrid; }
+int prefill_wgmma_k_dim() { return K_DIM; }
+int prefill_wgmma_h_dim() { return H_DIM; }
+int prefill_wgmma_fused_renorm() { return 1; }
+int prefill_wgmma_router_mode() { return ROUTER_MODE; }
+int prefill_wgmma_n_group() { return N_GROUP; }
+int prefill_wgmma_topk_group() { return TOPK_GROUP; }
+int prefill_wgmma_n_up() { return N_UP; }
+int prefill_wgmma_n_half() { return N_HALF; }
+int prefill_wgmma_block_m() { return TILE_M; }
+int prefill_wgmma_tp_max_c() { return kTpMaxChunks; }
+int prefill_wgmma_tp_align() { return 32; }
+int prefill_wgmma_tp_mm() { return 8; }
+int prefill_wgmma_tp_has_devseq() { return 1; }
+int prefill_wgmma_tp_seq_bytes() { return static_cast<int>(sizeof(uint32_t)); }
+int prefill_wgmma_tp_has_residual() { return 1; }
+int prefill_wgmma_tp_pad_words(int nchunk, int ncomm, int world) { return (nchunk * ncomm + 1) * world; }
+int prefill_wgmma_up_pipe() { return SB; }
+int prefill_wgmma_dn_pipe() { return SB; }
+int prefill_wgmma_a_stages() { return SA; }
+int prefill_wgmma_shm_total() { return DYN_SMEM + static_cast<int>(sizeof(SharedState)); }
+
+// ---- additions of this build (new capability = new symbol)
+int prefill_wgmma_arch() { return 100; }
+int prefill_wgmma_block_threads() { return BLOCK; }
+int prefill_wgmma_stable_sort() { return 1; }
+// Byte offset of the 32-bit status word inside the workspace and the bytes that follow it
+// (status, abort flag, two detail words). 0 after a successful launch.
+int prefill_wgmma_status_offset() { return static_cast<int>(offsetof(Workspace, status)); }
+int prefill_wgmma_status_bytes() { return 16; }
+int prefill_wgmma_counts_offset() { return static_cast<int>(offsetof(Workspace, expert_counts)); }
+int prefill_wgmma_offsets_offset() { return static_cast<int>(offsetof(Workspace, expert_offsets)); }
+int prefill_wgmma_total_tiles_offset() { return static_cast<int>(offsetof(Workspace, total_tiles)); }
+int prefill_wgmma_phase_ns_offset() { return static_cast<int>(offsetof(Workspace, phase_ns)); }
+// Upper bound, in microseconds, of every device-side wait of later launches.
+void prefill_wgmma_set_wait_timeout_us(unsigned long long us) { g_timeout_ns = us * 1000ull; }
+// Debug dump targets for later launches (device pointers, or null to switch off):
+// acc [T*8, N_UP] fp32 raw gate|up sums, inter [T*8, N_HALF] e4m3, inter_scale [T*8, N_HALF/128] fp32,
+// all indexed by sorted row.
+void prefill_wgmma_set_debug(void* acc, void* inter, void* inter_scale) {
+  g_dbg_acc = static_cast<float*>(acc);
+  g_dbg_inter = static_cast<uint8_t*>(inter);
+  g_dbg_inter_scale = static_cast<float*>(inter_scale);
+}
+
+int launch_prefill_moe_wgmma_q1_ep2(const float* logits, int num_tokens, int block_m, void* workspace,
+                                    size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
+                                    float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
+                                    const uint8_t* down_w_fp8, const float* down_w_scales, float* output_accum,
+                                    int32_t* topk_ids, float* topk_weights, int32_t* sorted_token_ids,
+                                    void* bf16_output, const float* router_bias, void* tp_mc, void* tp_pads,
+                                    int tp_rank, int tp_world, int tp_nchunk, int tp_ncomm, uint32_t tp_seq,
+                                    void* tp_seqctr, const void* tp_residual, float out_scale,
+                                    const int32_t* expert_map, cudaStream_t stream) {
+  (void)block_m;  // the tile height is the compiled TILE_M
+  if (EP_BUILD && expert_map == nullptr) return -120;
+  if (!EP_BUILD && expert_map != nullptr) return -121;
+  if (workspace == nullptr || workspace_bytes < sizeof(Workspace)) return -100;
+  if (num_tokens <= 0) return -101;
+  const long long numel = static_cast<long long>(num_tokens) * TOP_K;
+  if (numel / TILE_M + E_LOCAL > MAX_TILES) return -102;
+  if (logits == nullptr || act_bf16 == nullptr || act_fp8 == nullptr || act_scales == nullptr ||
+      up_w_fp8 == nullptr || up_w_scales == nullptr || down_w_fp8 == nullptr || down_w_scales == nullptr ||
+      output_accum == nullptr || topk_ids == nullptr || topk_weights == nullptr || sorted_token_ids == nullptr ||
+      bf16_output == nullptr)
+    return -104;
+  if (tp_mc != nullptr && tp_ncomm > 0) {
+    if (tp_nchunk < 1 || tp_nchunk > kTpMaxChunks) return -110;
+    if (tp_ncomm >= kGrid) return -111;
+    if (tp_world < 1 || tp_rank < 0 || tp_rank >= tp_world) return -112;
+    if (tp_pads == nullptr) return -113;
+    if ((static_cast<size_t>(num_tokens) * H_DIM) % (8 * static_cast<size_t>(tp_nchunk))) return -114;
+  }
+
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  int sm_count = 0;
+  err = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  if (sm_count < kGrid) return -103;
+
+  Params p{};
+  p.logits = logits;
+  p.num_tokens = num_tokens;
+  p.ws = static_cast<Workspace*>(workspace);
+  p.topk_ids = topk_ids;
+  p.topk_weights = topk_weights;
+  p.sorted_ids = sorted_token_ids;
+  p.act_bf16 = static_cast<const __nv_bfloat16*>(act_bf16);
+  p.act_fp8 = act_fp8;
+  p.act_scales = act_scales;
+  p.up_w_scales = up_w_scales;
+  p.down_w_scales = down_w_scales;
+  p.partial = reinterpret_cast<__nv_bfloat16*>(output_accum);
+  p.out = static_cast<__nv_bfloat16*>(bf16_output);
+  p.router_bias = router_bias;
+  p.expert_map = expert_map;
+  p.tp_mc = static_cast<__nv_bfloat16*>(tp_mc);
+  p.tp_pads = static_cast<uint32_t**>(tp_pads);
+  p.tp_rank = tp_rank;
+  p.tp_world = tp_world;
+  p.tp_nchunk = tp_nchunk;
+  p.tp_ncomm = tp_ncomm;
+  p.tp_seq = tp_seq;
+  p.tp_seqctr = static_cast<uint32_t*>(tp_seqctr);
+  p.residual = static_cast<const __nv_bfloat16*>(tp_residual);
+  p.out_scale = out_scale;
+  p.timeout_ns = g_timeout_ns;
+  p.dbg_acc = g_dbg_acc;
+  p.dbg_inter = g_dbg_inter;
+  p.dbg_inter_scale = g_dbg_inter_scale;
+
+  int rc = make_weight_map(&p.tm_up, up_w_fp8, static_cast<uint64_t>(E_LOCAL) * N_UP, K_DIM);
+  if (rc != 0) {
+    fprintf(stderr, "up-projection tensor map failed: %d\n", rc);
+    return -2;
+  }
+  rc = make_weight_map(&p.tm_down, down_w_fp8, static_cast<uint64_t>(E_LOCAL) * H_DIM, N_HALF);
+  if (rc != 0) {
+    fprintf(stderr, "down-projection tensor map failed: %d\n", rc);
+    return -3;
+  }
+
+  err = cudaFuncSetAttribute(moe_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  err = cudaMemsetAsync(workspace, 0, sizeof(Workspace), stream);
+  if (err != cudaSuccess) return static_cast<int>(err);
+
+  moe_prefill_kernel<<<kGrid, BLOCK, DYN_SMEM, stream>>>(p);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    fprintf(stderr, "kernel launch failed: %s\n", cudaGetErrorString(err));
+    return static_cast<int>(err);
+  }
+  return 0;
+}
+
+int launch_prefill_moe_wgmma_q1_tp2(const float* logits, int num_tokens, int block_m, void* workspace,
+                                    size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
+                                    float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
+                                    const uint8_t* down_w_fp8, const float* down_w_scales, float* output_accum,
+                                    int32_t* topk_ids, float* topk_weights, int32_t* sorted_token_ids,
+                                    void* bf16_output, const float* router_bias, void* tp_mc, void* tp_pads,
+                                    int tp_rank, int tp_world, int tp_nchunk, int tp_ncomm, uint32_t tp_seq,
+                                    void* tp_seqctr, const void* tp_residual, float out_scale,
+                                    cudaStream_t stream) {
+  return launch_prefill_moe_wgmma_q1_ep2(logits, num_tokens, block_m, workspace, workspace_bytes, act_bf16, act_fp8,
+                                         act_scales, up_w_fp8, up_w_scales, down_w_fp8, down_w_scales, output_accum,
+                                         topk_ids, topk_weights, sorted_token_ids, bf16_output, router_bias, tp_mc,
+                                         tp_pads, tp_rank, tp_world, tp_nchunk, tp_ncomm, tp_seq, tp_seqctr,
+                                         tp_residual, out_scale, nullptr, stream);
+}
+
+int launch_prefill_moe_wgmma_q1_tp(const float* logits, int num_tokens, int block_m, void* workspace,
+                                   size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8, float* act_scales,
+                                   const uint8_t* up_w_fp8, const float* up_w_scales, const uint8_t* down_w_fp8,
+                                   const float* down_w_scales, float* output_accum, int32_t* topk_ids,
+                                   float* topk_weights, int32_t* sorted_token_ids, void* bf16_output,
+                                   const float* router_bias, void* tp_mc, void* tp_pads, int tp_rank, int tp_world,
+                                   int tp_nchunk, int tp_ncomm, uint32_t tp_seq, void* tp_seqctr,
+                                   cudaStream_t stream) {
+  return launch_prefill_moe_wgmma_q1_tp2(logits, num_tokens, block_m, workspace, workspace_bytes, act_bf16, act_fp8,
+                                         act_scales, up_w_fp8, up_w_scales, down_w_fp8, down_w_scales, output_accum,
+                                         topk_ids, topk_weights, sorted_token_ids, bf16_output, router_bias, tp_mc,
+                                         tp_pads, tp_rank, tp_world, tp_nchunk, tp_ncomm, tp_seq, tp_seqctr, nullptr,
+                                         1.0f, stream);
+}
+
+int launch_prefill_moe_wgmma_q1_router(const float* logits, int num_tokens, int block_m, void* workspace,
+                                       size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
+                                       float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
+                                       const uint8_t* down_w_fp8, const float* down_w_scales, float* output_accum,
+                                       int32_t* topk_ids, float* topk_weights, int32_t* sorted_token_ids,
+                                       void* bf16_output, const float* router_bias, cudaStream_t stream) {
+  return launch_prefill_moe_wgmma_q1_tp(logits, num_tokens, block_m, workspace, workspace_bytes, act_bf16, act_fp8,
+                                        act_scales, up_w_fp8, up_w_scales, down_w_fp8, down_w_scales, output_accum,
+                                        topk_ids, topk_weights, sorted_token_ids, bf16_output, router_bias, nullptr,
+                                        nullptr, 0, 1, 1, 0, 0u, nullptr, stream);
+}
+
+int launch_prefill_moe_wgmma_q1(const float* logits, int num_tokens, int block_m, void* workspace,
+                                size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8, float* act_scales,
+                                const uint8_t* up_w_fp8, const float* up_w_scales, const uint8_t* down_w_fp8,
+                                const float* down_w_scales, float* output_accum, int32_t* topk_ids,
+                                float* topk_weights, int32_t* sorted_token_ids, void* bf16_output,
+                                cudaStream_t stream) {
+  return launch_prefill_moe_wgmma_q1_router(logits, num_tokens, block_m, workspace, workspace_bytes, act_bf16,
+                                            act_fp8, act_scales, up_w_fp8, up_w_scales, down_w_fp8, down_w_scales,
+                                            output_accum, topk_ids, topk_weights, sorted_token_ids, bf16_output,
+                                            nullptr, stream);
+}
+
+int launch_prefill_moe_wgmma_q1_ep(const float* logits, int num_tokens, int block_m, void* workspace,
+                                   size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8, float* act_scales,
+                                   const uint8_t* up_w_fp8, const float* up_w_scales, const uint8_t* down_w_fp8,
+                                   const float* down_w_scales, float* output_accum, int32_t* topk_ids,
+                                   float* topk_weights, int32_t* sorted_token_ids, void* bf16_output,
+                                   const float* router_bias, const int32_t* expert_map, cudaStream_t stream) {
+  return launch_prefill_moe_wgmma_q1_ep2(logits, num_tokens, block_m, workspace, workspace_bytes, act_bf16, act_fp8,
+                                         act_scales, up_w_fp8, up_w_scales, down_w_fp8, down_w_scales, output_accum,
+                                         topk_ids, topk_weights, sorted_token_ids, bf16_output, router_bias, nullptr,
+                                         nullptr, 0, 1, 1, 0, 0u, nullptr, nullptr, 1.0f, expert_map, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,452 @@
+"""Host side of the FP8 MoE prefill kernel: load the C-ABI library with ctypes, read its
+compiled geometry back, validate a call against it, own the scratch buffers, launch.
+
+Mirrors the reference's loader and launcher (vllm_integration/vllm/_custom_ops.py:4242-4994):
+same function names, argument meaning and error behaviour, so a maintainer can swap the
+module in behind ``Fp8MoEMethod.try_moe_monokernel``. Differences, all deliberate:
+
+* several binaries can be loaded in one process (one ``MonoKernel`` per .so); the
+  module-level functions act on the binary named by ``VLLM_PREFILL_MONOKERNEL_SO`` exactly
+  as the reference does, and refuse to guess when it is unset (_custom_ops.py:4259-4272);
+* scratch buffers are cached per (device, tokens) instead of being allocated on every call
+  (_custom_ops.py:4645-4652), and the per-slot partial buffer is bf16, the size the kernel
+  really touches;
+* every device-side wait of the kernel is bounded; ``check_status`` reads the status word.
+
+There is no CPU or library fallback: without CUDA and the compiled extension every launch
+raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+MOE_MONOKERNEL_PREFILL_MAX_TOKENS = 30720  # _custom_ops.py:4247
+
+_GEOMETRY_SYMBOLS = (
+    "num_experts", "num_experts_local", "ep_capable", "top_k", "k_dim", "h_dim", "n_up", "n_half",
+    "router_mode", "max_tiles", "grid_size", "fused_renorm", "block_m", "n_group", "topk_group",
+    "up_pipe", "dn_pipe", "a_stages", "shm_total", "arch", "block_threads", "stable_sort",
+)
+_TP_CAP_SYMBOLS = ("tp_max_c", "tp_has_residual", "tp_align", "tp_mm", "tp_has_devseq", "tp_seq_bytes", "grid_size")
+
+STATUS_CODES = {
+    0: "ok", 1: "grid barrier timed out", 2: "pipeline barrier timed out", 3: "chunk-ready wait timed out",
+    4: "rank barrier timed out", 5: "done-flag wait timed out", 6: "device index out of bounds",
+}
+
+
+def variant_path(variant: str) -> str:
+    """Path of the in-tree binary built for a named geometry (see unimonomoe_b200/build.py)."""
+    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", f"libprefill_mono_{variant}.so")
+
+
+class MonoKernel:
+    """One loaded ``libprefill_mono_*.so``."""
+
+    def __init__(self, so_path: str):
+        if not so_path:
+            raise RuntimeError(
+                "no monokernel binary selected; the compiled geometry of the kernel has to be the "
+                "caller's explicit choice (set VLLM_PREFILL_MONOKERNEL_SO)")
+        if not os.path.exists(so_path):
+            raise RuntimeError(f"monokernel binary {so_path} does not exist; build it with "
+                               "`python -m unimonomoe_b200.build`")
+        self.path = so_path
+        lib = ctypes.CDLL(so_path)
+        self.lib = lib
+        lib.launch_prefill_moe_wgmma_q1.restype = ctypes.c_int
+        lib.prefill_wgmma_workspace_bytes.restype = ctypes.c_size_t
+        self.has_router = self._bind("launch_prefill_moe_wgmma_q1_router")
+        self.has_tp = self._bind("launch_prefill_moe_wgmma_q1_tp")
+        self.has_tp2 = self._bind("launch_prefill_moe_wgmma_q1_tp2")
+        self.has_ep = self._bind("launch_prefill_moe_wgmma_q1_ep")
+        self._caps = {}
+        for name in _TP_CAP_SYMBOLS:
+            self._caps[name] = self._int_symbol(name)
+        try:
+            fn = lib.prefill_wgmma_tp_pad_words
+            fn.restype = ctypes.c_int
+            fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int]
+            self._pad_words_fn = fn
+        except AttributeError:
+            self._pad_words_fn = None
+        self._geo = None
+        self._scratch = {}
+        try:
+            lib.prefill_wgmma_set_wait_timeout_us.argtypes = [ctypes.c_ulonglong]
+            lib.prefill_wgmma_set_wait_timeout_us.restype = None
+            lib.prefill_wgmma_set_debug.argtypes = [ctypes.c_void_p] * 3
+            lib.prefill_wgmma_set_debug.restype = None
+        except AttributeError:
+            pass
+
+    # ------------------------------------------------------------------ symbols
+    def _bind(self, name: str) -> bool:
+        try:
+            getattr(self.lib, name).restype = ctypes.c_int
+            return True
+        except AttributeError:
+            return False
+
+    def _int_symbol(self, name: str):
+        try:
+            fn = getattr(self.lib, "prefill_wgmma_" + name)
+        except AttributeError:
+            return None
+        fn.restype = ctypes.c_int
+        return int(fn())
+
+    def geometry(self) -> dict:
+        """Compiled geometry; symbols the binary lacks come back None (_custom_ops.py:4443-4458)."""
+        if self._geo is None:
+            geo = {n: self._int_symbol(n) for n in _GEOMETRY_SYMBOLS}
+            geo["has_router_entry"] = self.has_router
+            geo["workspace_bytes"] = int(self.lib.prefill_wgmma_workspace_bytes())
+            self._geo = geo
+        return dict(self._geo)
+
+    def tp_caps(self) -> dict:
+        """Fused tensor-parallel capability (_custom_ops.py:4352-4376)."""
+        caps = dict(self._caps)
+        caps["has_tp"] = self.has_tp
+        caps["has_tp2_entry"] = self.has_tp2
+        caps["has_tp_residual"] = bool(self.has_tp2 and caps.get("tp_has_residual"))
+        caps["usable"] = bool(self.has_tp and self._pad_words_fn is not None and caps.get("tp_max_c")
+                              and caps.get("tp_align") and caps.get("grid_size"))
+        return caps
+
+    def tp_pad_words(self, nchunk: int, ncomm: int, world: int) -> int:
+        if self._pad_words_fn is None:
+            raise RuntimeError("loaded monokernel .so does not export prefill_wgmma_tp_pad_words, "
+                               "so it cannot drive the fused TP path")
+        return int(self._pad_words_fn(int(nchunk), int(ncomm), int(world)))
+
+    def set_wait_timeout_us(self, us: int) -> None:
+        self.lib.prefill_wgmma_set_wait_timeout_us(ctypes.c_ulonglong(int(us)))
+
+    def set_debug(self, acc=None, inter=None, inter_scale=None) -> None:
+        f = lambda t: ctypes.c_void_p(0 if t is None else t.data_ptr())  # noqa: E731
+        self.lib.prefill_wgmma_set_debug(f(acc), f(inter), f(inter_scale))
+
+    # ------------------------------------------------------------------ validation
+    def validate(self, activations_in, expert_weights_up, expert_weights_down, top_k, e_score_correction_bias,
+                 expert_map=None):
+        """Check this binary against these weights and return the bias to use
+        (_custom_ops.py:4461-4565). Raises RuntimeError on any mismatch."""
+        geo = self.geometry()
+        w13_n, w2_n = expert_weights_up.size(1), expert_weights_down.size(2)
+        if geo["n_up"] is not None and geo["n_up"] != w13_n:
+            raise RuntimeError(f"monokernel built for N_UP={geo['n_up']} but w13 has {w13_n}")
+        if geo["n_half"] is not None and geo["n_half"] != w2_n:
+            raise RuntimeError(f"monokernel built for N_HALF={geo['n_half']} but w2 has {w2_n}")
+        if geo["k_dim"] not in (None, activations_in.size(1)):
+            raise RuntimeError(f"monokernel built for K_DIM={geo['k_dim']} but activations have "
+                               f"{activations_in.size(1)}")
+        if geo["h_dim"] not in (None, expert_weights_down.size(1)):
+            raise RuntimeError(f"monokernel built for H_DIM={geo['h_dim']} but w2 has {expert_weights_down.size(1)} rows")
+        n_e = geo["num_experts"]
+        n_local = geo["num_experts_local"] if geo["num_experts_local"] is not None else n_e
+        n_got = expert_weights_up.size(0)
+        if n_local is not None and n_local != n_got:
+            raise RuntimeError(f"monokernel built to index {n_local} local expert slabs but got {n_got}")
+        if expert_map is None:
+            if n_e is not None and n_e != n_got:
+                raise RuntimeError(f"monokernel built for E={n_e} but got {n_got} experts and no expert_map "
+                                   "to remap them")
+        else:
+            if not geo["ep_capable"]:
+                raise RuntimeError("an expert_map was supplied but the loaded monokernel .so is not EP capable; "
+                                   "its weight indexing would use global expert ids")
+            if expert_map.dtype != torch.int32:
+                raise RuntimeError(f"expert_map must be int32, got {expert_map.dtype}")
+            if n_e is not None and expert_map.numel() != n_e:
+                raise RuntimeError(f"monokernel built for E={n_e} but expert_map has {expert_map.numel()} entries")
+        if geo["top_k"] not in (None, int(top_k)):
+            raise RuntimeError(f"monokernel built for TOP_K={geo['top_k']} but got top_k={top_k}")
+        bias = e_score_correction_bias
+        if bias is not None:
+            if geo["router_mode"] == 0:
+                raise RuntimeError("monokernel .so is a softmax (ROUTER_MODE 0) build and cannot apply an "
+                                   "e_score_correction_bias")
+            if not self.has_router:
+                raise RuntimeError("monokernel .so does not export launch_prefill_moe_wgmma_q1_router, so a "
+                                   "correction bias cannot be passed")
+            return bias.float().contiguous()
+        if geo["router_mode"] not in (None, 0):
+            raise RuntimeError(f"monokernel .so is a ROUTER_MODE {geo['router_mode']} (sigmoid) build but no "
+                               "e_score_correction_bias was supplied")
+        return None
+
+    # ------------------------------------------------------------------ scratch
+    def scratch(self, M: int, device) -> dict:
+        """Caller-owned scratch for M tokens on device, created once and reused."""
+        geo = self.geometry()
+        key = (str(device), int(M))
+        sc = self._scratch.get(key)
+        if sc is None:
+            K, H, k = geo["k_dim"], geo["h_dim"], geo["top_k"]
+            sc = {
+                "workspace": torch.zeros(geo["workspace_bytes"], dtype=torch.uint8, device=device),
+                "act_fp8": torch.empty(M, K, dtype=torch.uint8, device=device),
+                "act_scales": torch.empty(M, K // 128, dtype=torch.float32, device=device),
+                "topk_ids": torch.empty(M, k, dtype=torch.int32, device=device),
+                "topk_weights": torch.empty(M, k, dtype=torch.float32, device=device),
+                "sorted_ids": torch.empty(M * k, dtype=torch.int32, device=device),
+                "partial": torch.empty(M * k, H, dtype=torch.bfloat16, device=device),
+            }
+            if len(self._scratch) >= 4:
+                self._scratch.pop(next(iter(self._scratch)))
+            self._scratch[key] = sc
+        return sc
+
+    def check_status(self, workspace: torch.Tensor) -> None:
+        """Synchronise and raise if the last launch on this workspace reported a bounded-wait error."""
+        off = self._int_symbol("status_offset")
+        torch.cuda.synchronize(workspace.device)
+        words = workspace[off:off + 16].cpu().view(torch.int32).tolist()
+        st = words[0] & 0xFFFFFFFF
+        if st != 0:
+            code, site, block = st >> 24, (st >> 16) & 0xFF, st & 0xFFFF
+            raise RuntimeError(f"monokernel device status: {STATUS_CODES.get(code, code)} "
+                               f"(code {code}, site {site}, block {block}, aux {words[2]}, {words[3]})")
+
+    def workspace_view(self, workspace: torch.Tensor) -> dict:
+        """Decoded read-back of the counters the kernel leaves in the workspace."""
+        E = self.geometry()["num_experts"]
+        w = workspace.cpu()
+        g = lambda name, n, dt: w[self._int_symbol(name):self._int_symbol(name) + n * dt.itemsize].view(dt)  # noqa: E731
+        return {
+            "expert_counts": g("counts_offset", E, torch.int32).clone(),
+            "expert_offsets": g("offsets_offset", E + 1, torch.int32).clone(),
+            "total_tiles": int(g("total_tiles_offset", 1, torch.int32)[0]),
+            "phase_ns": g("phase_ns_offset", 8, torch.int64).clone(),
+        }
+
+    # ------------------------------------------------------------------ launch
+    def prefill_impl(self, activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
+                     expert_scales_down, top_k, renormalize, e_score_correction_bias, out, tp=None, residual=None,
+                     out_scale=1.0, expert_map=None, scratch=None, check=False) -> dict:
+        """Launch the kernel into ``out`` (_custom_ops.py:4568-4762). Returns the scratch dict
+        (topk_ids, topk_weights, sorted_ids, workspace, ...) the launch wrote."""
+        if not torch.cuda.is_available() or not activations_in.is_cuda:
+            raise RuntimeError("the FP8 MoE prefill kernel needs a CUDA device; there is no CPU path")
+        M, K = activations_in.shape
+        H = expert_weights_down.size(1)
+        top_k = int(top_k)
+        device = activations_in.device
+        if M > MOE_MONOKERNEL_PREFILL_MAX_TOKENS:
+            raise RuntimeError(f"monokernel refuses {M} tokens (cap {MOE_MONOKERNEL_PREFILL_MAX_TOKENS})")
+
+        act = activations_in.contiguous()
+        if act.dtype != torch.bfloat16:
+            raise RuntimeError(f"monokernel activations must be bfloat16, got {act.dtype}")
+        logits = router_logits.float().contiguous()
+        w_up = expert_weights_up.contiguous().view(torch.uint8)
+        w_down = expert_weights_down.contiguous().view(torch.uint8)
+        s_up = expert_scales_up.float().contiguous()
+        s_down = expert_scales_down.float().contiguous()
+
+        emap = None
+        if expert_map is not None:
+            if tp is not None:
+                raise RuntimeError("the fused TP collective and an expert_map cannot be combined; an EP rank's "
+                                   "output is reduced by the caller")
+            emap = expert_map.to(torch.int32).contiguous()
+        bias = self.validate(activations_in, expert_weights_up, expert_weights_down, top_k,
+                             e_score_correction_bias, emap)
+        if out.shape != (M, H) or out.dtype != torch.bfloat16:
+            raise RuntimeError(f"monokernel destination must be [{M}, {H}] bfloat16, got {tuple(out.shape)} {out.dtype}")
+        if not out.is_contiguous():
+            raise RuntimeError("monokernel destination must be contiguous")
+
+        resid_ptr = 0
+        if residual is not None:
+            if residual.shape != (M, H) or residual.dtype != torch.bfloat16:
+                raise RuntimeError(f"monokernel folded residual must be [{M}, {H}] bfloat16, got "
+                                   f"{tuple(residual.shape)} {residual.dtype}")
+            if not residual.is_contiguous():
+                raise RuntimeError("monokernel folded residual must be contiguous")
+            if tp is None:
+                raise RuntimeError("a folded residual is only carried by the fused collective; without a TP "
+                                   "configuration there is nothing to fold it into")
+            resid_ptr = residual.data_ptr()
+        fold = resid_ptr != 0 or float(out_scale) != 1.0
+        if fold and not self.has_tp2:
+            raise RuntimeError("loaded monokernel .so has no launch_prefill_moe_wgmma_q1_tp2, so it cannot fold a "
+                               "residual or apply an output scale")
+        if not renormalize and self.geometry()["fused_renorm"]:
+            raise RuntimeError("monokernel .so is a FUSED_RENORM build but renormalize=False was requested; the "
+                               "in-kernel normalization cannot be undone")
+
+        sc = scratch if scratch is not None else self.scratch(M, device)
+        vp = ctypes.c_void_p
+        args = [
+            vp(logits.data_ptr()), ctypes.c_int(M), ctypes.c_int(128),
+            vp(sc["workspace"].data_ptr()), ctypes.c_size_t(sc["workspace"].numel()),
+            vp(act.data_ptr()), vp(sc["act_fp8"].data_ptr()), vp(sc["act_scales"].data_ptr()),
+            vp(w_up.data_ptr()), vp(s_up.data_ptr()), vp(w_down.data_ptr()), vp(s_down.data_ptr()),
+            vp(sc["partial"].data_ptr()), vp(sc["topk_ids"].data_ptr()), vp(sc["topk_weights"].data_ptr()),
+            vp(sc["sorted_ids"].data_ptr()), vp(out.data_ptr()),
+        ]
+        bias_arg = vp(bias.data_ptr() if bias is not None else 0)
+        if tp is not None:
+            mc, pads, seqctr, rank, world, nchunk, ncomm = tp
+            entry = self.lib.launch_prefill_moe_wgmma_q1_tp2 if fold else self.lib.launch_prefill_moe_wgmma_q1_tp
+            args += [bias_arg, vp(int(mc)), vp(int(pads)), ctypes.c_int(int(rank)), ctypes.c_int(int(world)),
+                     ctypes.c_int(int(nchunk)), ctypes.c_int(int(ncomm)), ctypes.c_uint(0), vp(int(seqctr))]
+            if fold:
+                args += [vp(int(resid_ptr)), ctypes.c_float(float(out_scale))]
+        elif emap is not None:
+            if not self.has_ep:
+                raise RuntimeError("loaded monokernel .so has no launch_prefill_moe_wgmma_q1_ep")
+            entry = self.lib.launch_prefill_moe_wgmma_q1_ep
+            args += [bias_arg, vp(emap.data_ptr())]
+        elif bias is not None:
+            entry = self.lib.launch_prefill_moe_wgmma_q1_router
+            args += [bias_arg]
+        else:
+            entry = self.lib.launch_prefill_moe_wgmma_q1
+        args.append(vp(torch.cuda.current_stream(device).cuda_stream))
+        rc = entry(*args)
+        if rc != 0:
+            raise RuntimeError(f"launch_prefill_moe_wgmma_q1 failed: rc={rc}")
+        # keep the converted inputs alive until the stream has consumed them
+        sc["_keepalive"] = (act, logits, w_up, w_down, s_up, s_down, bias, emap)
+        if check:
+            self.check_status(sc["workspace"])
+        return sc
+
+    def prefill(self, activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
+                expert_scales_down, top_k=8, renormalize=True, e_score_correction_bias=None, expert_map=None,
+                check=False) -> torch.Tensor:
+        """Allocating variant (_custom_ops.py:4820-4858). Under EP the result is this rank's partial sum."""
+        M, H = activations_in.size(0), expert_weights_down.size(1)
+        out = torch.empty(M, H, dtype=torch.bfloat16, device=activations_in.device)
+        self.prefill_impl(activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
+                          expert_scales_down, top_k, renormalize, e_score_correction_bias, out, None, None, 1.0,
+                          expert_map, check=check)
+        return out
+
+    def prefill_out(self, activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
+                    expert_scales_down, out, top_k=8, renormalize=True, e_score_correction_bias=None, tp_mc_ptr=0,
+                    tp_pads_ptr=0, tp_seqctr_ptr=0, tp_rank=0, tp_world=1, tp_nchunk=0, tp_ncomm=0, tp_residual=None,
+                    tp_out_scale=1.0, check=False) -> None:
+        """Write into a caller-supplied destination (_custom_ops.py:4861-4924). tp_ncomm > 0 selects the
+        fused collective, in which case ``out`` must be the symmetric window tp_mc_ptr aliases."""
+        tp = None
+        if tp_ncomm > 0:
+            if not (tp_mc_ptr and tp_pads_ptr):
+                raise RuntimeError("fused TP launch requires both a multicast pointer and a barrier pad pointer")
+            tp = (tp_mc_ptr, tp_pads_ptr, tp_seqctr_ptr, tp_rank, tp_world, tp_nchunk, tp_ncomm)
+        self.prefill_impl(activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
+                          expert_scales_down, top_k, renormalize, e_score_correction_bias, out, tp, tp_residual,
+                          tp_out_scale, check=check)
+
+
+# ---------------------------------------------------------------------- module-level mirror
+_prefill_monokernel_lib: Optional[MonoKernel] = None
+
+
+def _load_prefill_monokernel() -> MonoKernel:
+    """The binary named by VLLM_PREFILL_MONOKERNEL_SO; refuses an unset variable
+    (_custom_ops.py:4253-4288)."""
+    global _prefill_monokernel_lib
+    if _prefill_monokernel_lib is None:
+        path = os.environ.get("VLLM_PREFILL_MONOKERNEL_SO")
+        if not path:
+            raise RuntimeError("VLLM_PREFILL_MONOKERNEL_SO is not set, so no monokernel binary has been selected; "
+                               "the compiled geometry of the kernel has to be the caller's explicit choice")
+        _prefill_monokernel_lib = MonoKernel(path)
+    return _prefill_monokernel_lib
+
+
+def _reset_prefill_monokernel() -> None:
+    global _prefill_monokernel_lib
+    _prefill_monokernel_lib = None
+
+
+def prefill_monokernel_geometry() -> dict:
+    return _load_prefill_monokernel().geometry()
+
+
+def prefill_monokernel_tp_caps() -> dict:
+    return _load_prefill_monokernel().tp_caps()
+
+
+def prefill_monokernel_tp_pad_words(nchunk: int, ncomm: int, world: int) -> int:
+    return _load_prefill_monokernel().tp_pad_words(nchunk, ncomm, world)
+
+
+def monokernel_validate(activations_in, expert_weights_up, expert_weights_down, top_k, e_score_correction_bias,
+                        expert_map=None):
+    return _load_prefill_monokernel().validate(activations_in, expert_weights_up, expert_weights_down, top_k,
+                                               e_score_correction_bias, expert_map)
+
+
+def moe_monokernel_prefill(activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
+                           expert_scales_down, top_k: int = 8, renormalize: bool = True,
+                           e_score_correction_bias=None, expert_map=None) -> torch.Tensor:
+    return _load_prefill_monokernel().prefill(activations_in, router_logits, expert_weights_up, expert_scales_up,
+                                              expert_weights_down, expert_scales_down, top_k, renormalize,
+                                              e_score_correction_bias, expert_map)
+
+
+def moe_monokernel_prefill_out(activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
+                               expert_scales_down, out, top_k: int = 8, renormalize: bool = True,
+                               e_score_correction_bias=None, tp_mc_ptr: int = 0, tp_pads_ptr: int = 0,
+                               tp_seqctr_ptr: int = 0, tp_rank: int = 0, tp_world: int = 1, tp_nchunk: int = 0,
+                               tp_ncomm: int = 0, tp_residual=None, tp_out_scale: float = 1.0) -> None:
+    _load_prefill_monokernel().prefill_out(activations_in, router_logits, expert_weights_up, expert_scales_up,
+                                           expert_weights_down, expert_scales_down, out, top_k, renormalize,
+                                           e_score_correction_bias, tp_mc_ptr, tp_pads_ptr, tp_seqctr_ptr, tp_rank,
+                                           tp_world, tp_nchunk, tp_ncomm, tp_residual, tp_out_scale)
+
+
+def _register_ops() -> None:
+    """torch custom ops with fake implementations, as the reference registers them
+    (_custom_ops.py:4953-4994): the functional op returns a fresh tensor, the ``_out`` op
+    declares that it mutates ``out`` so repeated calls on one buffer stay ordered."""
+    try:
+        @torch.library.custom_op("unimonomoe::moe_monokernel_prefill", mutates_args=())
+        def _op(activations_in: torch.Tensor, router_logits: torch.Tensor, expert_weights_up: torch.Tensor,
+                expert_scales_up: torch.Tensor, expert_weights_down: torch.Tensor, expert_scales_down: torch.Tensor,
+                top_k: int = 8, renormalize: bool = True, e_score_correction_bias: Optional[torch.Tensor] = None,
+                expert_map: Optional[torch.Tensor] = None) -> torch.Tensor:
+            return moe_monokernel_prefill(activations_in, router_logits, expert_weights_up, expert_scales_up,
+                                          expert_weights_down, expert_scales_down, top_k, renormalize,
+                                          e_score_correction_bias, expert_map)
+
+        @_op.register_fake
+        def _(activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
+              expert_scales_down, top_k=8, renormalize=True, e_score_correction_bias=None, expert_map=None):
+            return torch.empty((activations_in.size(0), expert_weights_down.size(1)), dtype=torch.bfloat16,
+                               device=activations_in.device)
+
+        @torch.library.custom_op("unimonomoe::moe_monokernel_prefill_out", mutates_args=("out",))
+        def _op_out(activations_in: torch.Tensor, router_logits: torch.Tensor, expert_weights_up: torch.Tensor,
+                    expert_scales_up: torch.Tensor, expert_weights_down: torch.Tensor,
+                    expert_scales_down: torch.Tensor, out: torch.Tensor, top_k: int = 8, renormalize: bool = True,
+                    e_score_correction_bias: Optional[torch.Tensor] = None, tp_mc_ptr: int = 0, tp_pads_ptr: int = 0,
+                    tp_seqctr_ptr: int = 0, tp_rank: int = 0, tp_world: int = 1, tp_nchunk: int = 0,
+                    tp_ncomm: int = 0, tp_residual: Optional[torch.Tensor] = None,
+                    tp_out_scale: float = 1.0) -> None:
+            moe_monokernel_prefill_out(activations_in, router_logits, expert_weights_up, expert_scales_up,
+                                       expert_weights_down, expert_scales_down, out, top_k, renormalize,
+                                       e_score_correction_bias, tp_mc_ptr, tp_pads_ptr, tp_seqctr_ptr, tp_rank,
+                                       tp_world, tp_nchunk, tp_ncomm, tp_residual, tp_out_scale)
+
+        @_op_out.register_fake
+        def _(activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
+              expert_scales_down, out, top_k=8, renormalize=True, e_score_correction_bias=None, tp_mc_ptr=0,
+              tp_pads_ptr=0, tp_seqctr_ptr=0, tp_rank=0, tp_world=1, tp_nchunk=0, tp_ncomm=0, tp_residual=None,
+              tp_out_scale=1.0):
+            return None
+    except Exception:  # already registered in this process
+        pass
+
+
+_register_ops()
