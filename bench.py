@@ -1,0 +1,351 @@
+"""Benchmark of the FP8 MoE prefill layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--impl ours|reference]
+
+One step = one pass of the layer (route -> sort -> up/SiLU/requant/down -> reduce) over one
+synthetic prefill batch. N=1 runs the Qwen3.5-35B-A3B-like layer (H=2048, E=256, top-8,
+I=512, block-FP8 weights) at T=16384 tokens; N=2/4 run the same layer tensor-parallel
+(I/N per rank), N=8 expert-parallel (32 experts per rank), output reduced across ranks.
+Prints ONE JSON line (rank 0). --impl reference times the reference's CPU path (torch MoE on
+dequantised weights, host cores) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from unimonomoe_b200 import MonoKernel, synth, variant_path  # noqa: E402
+
+NOMINAL_FP8_TFLOPS = 4500.0
+METRIC = "moe_layer_prefill_fp8_tflops"
+UNIT = "TFLOP/s"
+
+
+def measured_peaks() -> dict:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return json.load(open(p))
+        except Exception:
+            pass
+    return {}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.003)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join()
+
+    def summary(self) -> dict:
+        return {"sm_mhz": (statistics.median(self.samples) if self.samples else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except Exception:
+            return local
+    return local
+
+
+def fp8_gemm_tflops(dev) -> float | None:
+    """Library FP8 GEMM throughput (torch._scaled_mm e4m3 x e4m3 8192^3, best of 10): context for the
+    roofline, never part of a timed step."""
+    try:
+        n = 8192
+        a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=dev)
+        best = None
+        for i in range(13):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            if i >= 3:
+                best = ms if best is None else min(best, ms)
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception:
+        return None
+
+
+def cpu_reference_moe(spec, layer_cpu, hs, logits, threads: int, dtype=torch.float32):
+    """The reference's CPU path: softmax top-8 routing on the logits, then per expert
+    x @ W13^T -> SiLU(gate)*up -> @ W2^T on dequantised block-FP8 weights, weighted sum
+    (validation/ep4_acc.py:183-217), in torch on `threads` host threads."""
+    from oracle import cpu_oracle as O
+    torch.set_num_threads(threads)
+    top = torch.topk(logits, spec.top_k, dim=1)
+    w = torch.softmax(logits, 1).gather(1, top.indices)
+    w = w / w.sum(1, keepdim=True).clamp(min=1e-30)
+    return O.moe_fp64(hs, top.indices, w, layer_cpu["w13"], layer_cpu["w13_scale"], layer_cpu["w2"],
+                      layer_cpu["w2_scale"], dtype=dtype)
+
+
+def time_cpu_baseline(spec, sample_tokens: int, reps: int = 2) -> dict:
+    threads = os.cpu_count() or 1
+    layer = synth.make_layer(spec, seed=0, device="cpu", with_shared=False)
+    batch = synth.make_batch(spec, layer, sample_tokens, seed=0, device="cpu")
+    times = []
+    for _ in range(reps + 1):
+        t0 = time.perf_counter()
+        cpu_reference_moe(spec, layer, batch["hs"], batch["logits"], threads)
+        times.append(time.perf_counter() - t0)
+    sec = statistics.median(times[1:])
+    fl = synth.routed_flops(spec, sample_tokens)
+    return {"value": fl / sec / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{sample_tokens} tokens of the same layer (all 256 experts), torch fp32 on dequantised "
+                      f"weights, median of {reps} passes, {sec * 1e3:.0f} ms per pass",
+            "ms_per_step": sec * 1e3}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    spec = synth.QWEN
+    sample = 256
+    times = []
+    threads = os.cpu_count() or 1
+    layer = synth.make_layer(spec, seed=0, device="cpu", with_shared=False)
+    batch = synth.make_batch(spec, layer, sample, seed=0, device="cpu")
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        cpu_reference_moe(spec, layer, batch["hs"], batch["logits"], threads)
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    val = synth.routed_flops(spec, sample) / sec / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{spec.name} MoE layer, reference CPU path on a {sample}-token sample of the "
+                               f"T={args.tokens} batch", "tokens": args.tokens, "sample_tokens": sample},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{sample} tokens per step, torch fp32 dequantised MoE (validation/ep4_acc.py:183-217 restated)"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=16384)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else max(args.warmup, 1)
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernel has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    spec = synth.QWEN
+    T = args.tokens
+    if world == 1:
+        variant, par, kw = "qwen_w1", "none", {}
+    elif world in (2, 4):
+        variant, par = f"qwen_tp{world}", f"tp{world}"
+        n = spec.inter // world
+        kw = {"inter_slice": (rank * n, (rank + 1) * n)}
+    else:
+        variant, par = f"qwen_ep{world}", f"ep{world}"
+        n = spec.experts // world
+        kw = {"expert_slice": (rank * n, (rank + 1) * n)}
+    mk = MonoKernel(variant_path(variant))
+    layer = synth.make_layer(spec, seed=0, device=dev, with_shared=False, **kw)
+    emap = synth.expert_map(spec, rank, world, device=dev) if par.startswith("ep") else None
+    full_router = layer
+    batch = synth.make_batch(spec, full_router, T, seed=0, device=dev)
+    out = torch.empty(T, spec.hidden, dtype=torch.bfloat16, device=dev)
+    sc = mk.scratch(T, dev)
+
+    def step():
+        mk.prefill_impl(batch["hs"], batch["logits"], layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"],
+                        spec.top_k, True, None, out, expert_map=emap, scratch=sc)
+        if world > 1:
+            dist.all_reduce(out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    mk.check_status(sc["workspace"])
+
+    # ---- device-resident timing: K steps between two events, plus one event pair per kernel launch
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local)) as clk:
+        barrier()
+        e0.record()
+        for a, b in evs:
+            a.record()
+            mk.prefill_impl(batch["hs"], batch["logits"], layer["w13"], layer["w13_scale"], layer["w2"],
+                            layer["w2_scale"], spec.top_k, True, None, out, expert_map=emap, scratch=sc)
+            b.record()
+            if world > 1:
+                dist.all_reduce(out)
+        e1.record()
+        barrier()
+    total_ms = e0.elapsed_time(e1)
+    kern_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    mk.check_status(sc["workspace"])
+    t = torch.tensor([total_ms, kern_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, kern_ms = float(t[0]), float(t[1])
+    ms_per_step = total_ms / args.steps
+    flops = synth.routed_flops(spec, T)  # whole job: all ranks together
+    value = flops / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end through the public API: host buffers in, host result out, copies inside the timed region
+    hs_host = batch["hs"].cpu().pin_memory()
+    lg_host = batch["logits"].cpu().pin_memory()
+    out_host = torch.empty(T, spec.hidden, dtype=torch.bfloat16).pin_memory()
+    hs_dev, lg_dev = torch.empty_like(batch["hs"]), torch.empty_like(batch["logits"])
+
+    def e2e_step():
+        hs_dev.copy_(hs_host, non_blocking=True)
+        lg_dev.copy_(lg_host, non_blocking=True)
+        mk.prefill_impl(hs_dev, lg_dev, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k,
+                        True, None, out, expert_map=emap, scratch=sc)
+        if world > 1:
+            dist.all_reduce(out)
+        out_host.copy_(out, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    n_e2e = max(5, min(args.steps, 20))
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    e3.record()
+    barrier()
+    t = torch.tensor([e2.elapsed_time(e3) / n_e2e], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t[0])
+    h2d = hs_host.numel() * 2 + lg_host.numel() * 4
+    d2h = out_host.numel() * 2
+
+    if rank == 0:
+        peaks = measured_peaks()
+        fp8_lib = fp8_gemm_tflops(dev) if world == 1 else None
+        if peaks.get("bf16_tflops"):
+            peak, peak_src = 2.0 * float(peaks["bf16_tflops"]), "2 x bf16_tflops (burst) of MEASURED_PEAKS.json: no fp8 figure is measured there"
+        else:
+            peak, peak_src = 2.0 * 1590.0, "2 x 1590 TFLOP/s bf16 fallback"
+        achieved = (flops / world) / (kern_ms * 1e-3) / 1e12
+        traffic = None
+        tp = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(tp):
+            try:
+                traffic = json.load(open(tp)).get(f"{variant}_T{T}")
+            except Exception:
+                traffic = None
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": f"{spec.name} MoE layer prefill, T={T} tokens, H=2048, E=256, top-8, I=512, "
+                                   f"block-FP8 [128,128] weights", "tokens": T, "parallelism": par, "variant": variant,
+                       "l2_policy": "inputs larger than L2: 805 MB of weights + 0.5 GB of partial rows stream per step",
+                       "reduce": "none" if world == 1 else "NCCL all-reduce after the kernel"},
+            "clocks": clk.summary(),
+            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps,
+            "kernel_ms": kern_ms,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+                         "traffic": traffic, "peak_source": peak_src, "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
+                         "library_fp8_gemm_tflops": fp8_lib},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = time_cpu_baseline(spec, 256)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

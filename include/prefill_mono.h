@@ -1,0 +1,173 @@
+/* C ABI of libprefill_mono_<variant>.so -- the drop-in boundary of the FP8 MoE prefill
+ * kernel. Plain pointers and sizes only; every launch is asynchronous on the caller's
+ * stream, allocates nothing and keeps no state between calls. The caller owns every
+ * buffer, including the workspace. The symbols, argument order and return codes are the
+ * ones the reference's loader binds with ctypes
+ * (vllm_integration/vllm/_custom_ops.py:4274-4288, :4705-4743), so its gates and its vLLM
+ * quant-method hook work against this library unchanged.
+ *
+ * File references below are paths inside the reference repository;
+ * Q  = kernel/qwen_tp/src/prefill_mono_final_nb.cu
+ * EP = kernel/qwen_ep/src/prefill_mono_final_nb.cu
+ *
+ * Return codes of the launch entry points (Q:1569-1599, Q:1621-1638, EP:1658-1659):
+ *     0      launched
+ *  -100      workspace null or smaller than prefill_wgmma_workspace_bytes()
+ *  -101      num_tokens <= 0
+ *  -102      num_tokens*top_k/128 + local experts exceeds prefill_wgmma_max_tiles()
+ *  -103      device has fewer SMs than prefill_wgmma_grid_size()
+ *  -104      a required pointer is null
+ *  -110..-114 fused tensor-parallel arguments (chunk count, ncomm, rank/world, pads, chunk alignment)
+ *  -120      expert-parallel build called without an expert map
+ *  -121      non-expert-parallel build called with an expert map
+ *  -2 / -3   tensor-map encoding failed (up / down weights)
+ *  > 0       cudaError_t
+ * All negative codes are returned before any CUDA call is made.
+ *
+ * Buffers (T = num_tokens, k = top_k = 8, E = 256 routed experts, El = local experts):
+ *   logits            fp32 [T, E]                      in
+ *   workspace         >= prefill_wgmma_workspace_bytes(); zeroed by the launch itself
+ *   act_bf16          bf16 [T, K]                      in
+ *   act_fp8           u8   [T, K]                      scratch/out: e4m3 activations
+ *   act_scales        fp32 [T, K/128]                  scratch/out
+ *   up_w_fp8          e4m3 [El, 2*N_HALF, K]           gate rows then up rows
+ *   up_w_scales       fp32 [El, 2*N_HALF/128, K/128]
+ *   down_w_fp8        e4m3 [El, H, N_HALF]
+ *   down_w_scales     fp32 [El, H/128, N_HALF/128]
+ *   output_accum      >= T*k*H*2 bytes                 scratch: bf16 partial rows [T*k, H]
+ *   topk_ids          i32  [T, k]                      out (local ids, -1 = not on this rank)
+ *   topk_weights      fp32 [T, k]                      out (already renormalised)
+ *   sorted_token_ids  i32  [T*k]                       out: flat slots t*k+j grouped by expert,
+ *                                                      ascending inside an expert (stable)
+ *   bf16_output       bf16 [T, H]                      out
+ */
+#ifndef PREFILL_MONO_H_
+#define PREFILL_MONO_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* prefill_mono_stream_t; /* cudaStream_t */
+
+/* ---- launch entry points ------------------------------------------------------------ */
+
+/* Q:1726-1739. Routing from logits, no bias. */
+int launch_prefill_moe_wgmma_q1(const float* logits, int num_tokens, int block_m, void* workspace,
+                                size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8, float* act_scales,
+                                const uint8_t* up_w_fp8, const float* up_w_scales, const uint8_t* down_w_fp8,
+                                const float* down_w_scales, float* output_accum, int32_t* topk_ids,
+                                float* topk_weights, int32_t* sorted_token_ids, void* bf16_output,
+                                prefill_mono_stream_t stream);
+
+/* Q:1708-1722. Adds the per-expert selection bias of the sigmoid router modes (fp32 [E] or null). */
+int launch_prefill_moe_wgmma_q1_router(const float* logits, int num_tokens, int block_m, void* workspace,
+                                       size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
+                                       float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
+                                       const uint8_t* down_w_fp8, const float* down_w_scales, float* output_accum,
+                                       int32_t* topk_ids, float* topk_weights, int32_t* sorted_token_ids,
+                                       void* bf16_output, const float* router_bias, prefill_mono_stream_t stream);
+
+/* Q:1686-1703. Fused tensor-parallel epilogue: tp_mc is the multicast alias of bf16_output
+ * on a symmetric window, tp_pads a device array of per-rank base pointers of a separate
+ * symmetric barrier window of prefill_wgmma_tp_pad_words() words, tp_seqctr a caller-owned
+ * 4-byte device word zeroed once. tp_ncomm == 0 or tp_mc == null runs the ordinary kernel. */
+int launch_prefill_moe_wgmma_q1_tp(const float* logits, int num_tokens, int block_m, void* workspace,
+                                   size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8, float* act_scales,
+                                   const uint8_t* up_w_fp8, const float* up_w_scales, const uint8_t* down_w_fp8,
+                                   const float* down_w_scales, float* output_accum, int32_t* topk_ids,
+                                   float* topk_weights, int32_t* sorted_token_ids, void* bf16_output,
+                                   const float* router_bias, void* tp_mc, void* tp_pads, int tp_rank, int tp_world,
+                                   int tp_nchunk, int tp_ncomm, uint32_t tp_seq, void* tp_seqctr,
+                                   prefill_mono_stream_t stream);
+
+/* Q:1547-1568. _tp plus a bf16 [T,H] residual folded into the same reduce and an fp32 scale
+ * on the routed sum: out = bf16(out_scale * sum_k partial_k + residual). */
+int launch_prefill_moe_wgmma_q1_tp2(const float* logits, int num_tokens, int block_m, void* workspace,
+                                    size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
+                                    float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
+                                    const uint8_t* down_w_fp8, const float* down_w_scales, float* output_accum,
+                                    int32_t* topk_ids, float* topk_weights, int32_t* sorted_token_ids,
+                                    void* bf16_output, const float* router_bias, void* tp_mc, void* tp_pads,
+                                    int tp_rank, int tp_world, int tp_nchunk, int tp_ncomm, uint32_t tp_seq,
+                                    void* tp_seqctr, const void* tp_residual, float out_scale,
+                                    prefill_mono_stream_t stream);
+
+/* EP:1809-1823. Expert parallel: expert_map is i32 [E], local slot of each global expert or -1.
+ * The output is this rank's partial sum. */
+int launch_prefill_moe_wgmma_q1_ep(const float* logits, int num_tokens, int block_m, void* workspace,
+                                   size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8, float* act_scales,
+                                   const uint8_t* up_w_fp8, const float* up_w_scales, const uint8_t* down_w_fp8,
+                                   const float* down_w_scales, float* output_accum, int32_t* topk_ids,
+                                   float* topk_weights, int32_t* sorted_token_ids, void* bf16_output,
+                                   const float* router_bias, const int32_t* expert_map, prefill_mono_stream_t stream);
+
+/* EP:1627-1651. The superset entry every other one forwards to. */
+int launch_prefill_moe_wgmma_q1_ep2(const float* logits, int num_tokens, int block_m, void* workspace,
+                                    size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
+                                    float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
+                                    const uint8_t* down_w_fp8, const float* down_w_scales, float* output_accum,
+                                    int32_t* topk_ids, float* topk_weights, int32_t* sorted_token_ids,
+                                    void* bf16_output, const float* router_bias, void* tp_mc, void* tp_pads,
+                                    int tp_rank, int tp_world, int tp_nchunk, int tp_ncomm, uint32_t tp_seq,
+                                    void* tp_seqctr, const void* tp_residual, float out_scale,
+                                    const int32_t* expert_map, prefill_mono_stream_t stream);
+
+/* ---- compiled geometry and capabilities (host only, no CUDA call) -------------------- */
+
+size_t prefill_wgmma_workspace_bytes(void);   /* Q:1515 */
+int prefill_wgmma_num_experts(void);          /* Q:1516 */
+int prefill_wgmma_num_experts_local(void);    /* EP:1587 */
+int prefill_wgmma_ep_capable(void);           /* EP:1592 */
+int prefill_wgmma_top_k(void);                /* Q:1517 */
+int prefill_wgmma_max_tiles(void);            /* Q:1518 */
+int prefill_wgmma_grid_size(void);            /* Q:1519; 148 here */
+int prefill_wgmma_k_dim(void);                /* Q:1520 */
+int prefill_wgmma_h_dim(void);                /* Q:1521 */
+int prefill_wgmma_fused_renorm(void);         /* Q:1527; 1 = weights already renormalised */
+int prefill_wgmma_router_mode(void);          /* Q:1741; 0 softmax, 1 sigmoid+bias, 2 grouped */
+int prefill_wgmma_n_group(void);              /* Q:1742 */
+int prefill_wgmma_topk_group(void);           /* Q:1743 */
+int prefill_wgmma_n_up(void);                 /* Q:1748 */
+int prefill_wgmma_n_half(void);               /* Q:1749 */
+int prefill_wgmma_block_m(void);              /* Q:1754; rows per tile, 128 */
+int prefill_wgmma_tp_max_c(void);             /* Q:1764 */
+int prefill_wgmma_tp_align(void);             /* Q:1765 */
+int prefill_wgmma_tp_mm(void);                /* Q:1766 */
+int prefill_wgmma_tp_has_devseq(void);        /* Q:1771 */
+int prefill_wgmma_tp_seq_bytes(void);         /* Q:1774 */
+int prefill_wgmma_tp_has_residual(void);      /* Q:1779 */
+int prefill_wgmma_tp_pad_words(int nchunk, int ncomm, int world); /* Q:1782-1784 */
+int prefill_wgmma_up_pipe(void);              /* Q:1786; weight ring depth */
+int prefill_wgmma_dn_pipe(void);              /* Q:1787; weight ring depth (one ring serves both phases) */
+int prefill_wgmma_a_stages(void);             /* Q:1788; activation ring depth */
+int prefill_wgmma_shm_total(void);            /* Q:1789 */
+
+/* ---- additions of this library: no counterpart in the reference ---------------------- */
+
+int prefill_wgmma_arch(void);                 /* 100 = built for sm_100a */
+int prefill_wgmma_block_threads(void);        /* threads per CTA */
+int prefill_wgmma_stable_sort(void);          /* 1 = sorted_token_ids is deterministic (stable) */
+/* Bounded waits: every device-side wait gives up after the time limit, records
+ * (code << 24 | site << 16 | block) in the 32-bit status word of the workspace and the
+ * launch returns normally. Read the word after synchronising; 0 = success. */
+int prefill_wgmma_status_offset(void);
+int prefill_wgmma_status_bytes(void);
+void prefill_wgmma_set_wait_timeout_us(unsigned long long microseconds); /* later launches; default 2 s */
+/* Offsets of the read-back counters inside the workspace. */
+int prefill_wgmma_counts_offset(void);        /* i32 [E]   rows per local expert */
+int prefill_wgmma_offsets_offset(void);       /* i32 [E+1] exclusive prefix sum */
+int prefill_wgmma_total_tiles_offset(void);   /* i32 */
+int prefill_wgmma_phase_ns_offset(void);      /* u64 [8] %globaltimer at phase boundaries */
+/* Debug dump targets for later launches (device pointers or null): raw gate|up sums
+ * fp32 [T*k, 2*N_HALF], e4m3 intermediate [T*k, N_HALF], its scales fp32 [T*k, N_HALF/128],
+ * indexed by sorted row. */
+void prefill_wgmma_set_debug(void* acc, void* inter, void* inter_scale);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PREFILL_MONO_H_ */

@@ -1,0 +1,73 @@
+"""Shared helpers of the GPU parity tests: launch through the C-ABI, compare with the oracle."""
+import numpy as np
+import torch
+
+from unimonomoe_b200 import MonoKernel, synth, variant_path
+
+DEV = "cuda:0"
+# acceptance bounds of the output comparison against the path-faithful oracle
+MAX_ABS_OVER_RMS = 2e-2
+MIN_COS = 0.9995
+
+_KERNELS = {}
+
+
+def kernel(variant: str) -> MonoKernel:
+    if variant not in _KERNELS:
+        _KERNELS[variant] = MonoKernel(variant_path(variant))
+    return _KERNELS[variant]
+
+
+def launch(mk, layer, batch, expert_map=None, poison=True):
+    """One launch through the ctypes C-ABI; returns host copies of everything it wrote."""
+    T = batch["hs"].shape[0]
+    H = layer["w2"].shape[1]
+    out = torch.full((T, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    sc = mk.scratch(T, DEV)
+    if poison:
+        sc["partial"].fill_(float("nan"))
+        sc["sorted_ids"].fill_(-7)
+    mk.prefill_impl(batch["hs"], batch["logits"], layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"],
+                    8, True, layer.get("bias"), out, expert_map=expert_map, check=True)
+    wv = mk.workspace_view(sc["workspace"])
+    return {
+        "out": out, "ids": sc["topk_ids"].cpu().numpy(), "weights": sc["topk_weights"].cpu().numpy(),
+        "sorted": sc["sorted_ids"].cpu().numpy(), "act_q": sc["act_fp8"].cpu().numpy(),
+        "act_s": sc["act_scales"].cpu().numpy(), "counts": wv["expert_counts"].numpy(),
+        "offsets": wv["expert_offsets"].numpy(), "total_tiles": wv["total_tiles"],
+    }
+
+
+def check_routing(O, res, batch, mode, bias, n_local, expert_map=None):
+    """Expert ids, weights, counts, offsets and the sort permutation must be bit-exact."""
+    ids, w, gids = O.route(batch["logits"], mode=mode, bias=bias, expert_map=expert_map)
+    assert (res["ids"] == ids).all(), f"{int((res['ids'] != ids).any(1).sum())} tokens routed differently"
+    assert (res["weights"].view(np.uint32) == w.view(np.uint32)).all()
+    cnt, off, srt = O.sort_slots(ids, n_local)
+    assert (res["counts"][:n_local] == cnt).all()
+    assert (res["offsets"][:n_local + 1] == off).all()
+    assert (res["sorted"][:len(srt)] == srt).all()
+    assert res["total_tiles"] == int(((cnt + 127) // 128).sum())
+    return ids, w, gids
+
+
+def check_act_quant(O, res, batch):
+    q, s = O.quant_act(batch["hs"])
+    assert (res["act_q"] == q).all()
+    assert (res["act_s"].view(np.uint32) == s.view(np.uint32)).all()
+    return q, s
+
+
+def sample_tokens(T, n, seed=0):
+    if T <= n:
+        return np.arange(T, dtype=np.int32)
+    return np.sort(np.random.RandomState(seed).choice(T, n, replace=False)).astype(np.int32)
+
+
+def check_output(O, out, toks, q, s, ids, w, layer, **kw):
+    ref = O.moe_path(toks, q, s, ids, w, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], **kw)
+    got = out.float().cpu()[torch.from_numpy(toks).long()]
+    assert torch.isfinite(got).all()
+    m = O.parity_metrics(got, ref.float())
+    assert m["max_abs_over_rms"] <= MAX_ABS_OVER_RMS and m["cos"] >= MIN_COS, m
+    return m

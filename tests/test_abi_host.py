@@ -1,0 +1,173 @@
+"""C-ABI surface and host logic, CPU only: the libraries load without a GPU driver, export
+every symbol include/prefill_mono.h declares, report the geometry they were built for, and
+decline bad calls with the reference's return codes before any CUDA call."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from unimonomoe_b200 import MonoKernel, build, loader, synth, variant_path
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "prefill_mono.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b((?:launch_prefill_moe_wgmma|prefill_wgmma)\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(built_libs):
+    names = declared_symbols()
+    assert len(names) >= 40
+    for variant, path in built_libs.items():
+        lib = ctypes.CDLL(path)
+        missing = [n for n in names if not hasattr(lib, n)]
+        assert not missing, (variant, missing)
+
+
+@pytest.mark.parametrize("variant", list(build.VARIANTS))
+def test_geometry_readback(built_libs, variant):
+    g = build.VARIANTS[variant]
+    geo = MonoKernel(built_libs[variant]).geometry()
+    assert geo["k_dim"] == g["K"] and geo["h_dim"] == g["H"]
+    assert geo["n_half"] == g["N_HALF"] and geo["n_up"] == 2 * g["N_HALF"]
+    assert geo["num_experts"] == 256 and geo["num_experts_local"] == g["E_LOCAL"]
+    assert geo["ep_capable"] == int(g["E_LOCAL"] != 256)
+    assert geo["router_mode"] == g["MODE"] and geo["top_k"] == 8 and geo["fused_renorm"] == 1
+    assert geo["grid_size"] == 148 and geo["block_m"] == 128 and geo["arch"] == 100
+    assert geo["shm_total"] <= 227 * 1024
+    assert geo["a_stages"] >= 2 and geo["up_pipe"] >= 2
+    assert geo["workspace_bytes"] >= 148 * 256 * 4
+
+
+def _args(n_tokens=16, ws_bytes=None, null=None, extra=()):
+    """Argument list with small dummy host buffers: every call below must be declined before
+    the library touches CUDA, so the pointers are never dereferenced."""
+    buf = (ctypes.c_char * 64)()
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    a = [p, ctypes.c_int(n_tokens), ctypes.c_int(128), p, ctypes.c_size_t(1 << 20 if ws_bytes is None else ws_bytes)]
+    a += [p] * 12
+    if null is not None:
+        a[null] = ctypes.c_void_p(0)
+    return a + list(extra) + [ctypes.c_void_p(0)], buf
+
+
+def test_pre_launch_return_codes(built_libs):
+    lib = MonoKernel(built_libs["qwen_w1"]).lib
+    a, keep = _args(ws_bytes=16)
+    assert lib.launch_prefill_moe_wgmma_q1(*a) == -100
+    a, keep = _args(null=3)
+    assert lib.launch_prefill_moe_wgmma_q1(*a) == -100
+    a, keep = _args(n_tokens=0)
+    assert lib.launch_prefill_moe_wgmma_q1(*a) == -101
+    a, keep = _args(n_tokens=80000)
+    assert lib.launch_prefill_moe_wgmma_q1(*a) == -102
+    for idx in (0, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16):
+        a, keep = _args(null=idx)
+        assert lib.launch_prefill_moe_wgmma_q1(*a) == -104, idx
+    # fused tensor-parallel argument checks
+    vp, ci = ctypes.c_void_p, ctypes.c_int
+    buf = (ctypes.c_char * 64)()
+    p = ctypes.cast(buf, vp)
+
+    def tp(nchunk, ncomm, rank, world, pads=p, n_tokens=16):
+        a, k = _args(n_tokens=n_tokens, extra=[vp(0), p, pads, ci(rank), ci(world), ci(nchunk), ci(ncomm),
+                                               ctypes.c_uint(0), vp(0)])
+        return lib.launch_prefill_moe_wgmma_q1_tp(*a)
+
+    assert tp(0, 4, 0, 2) == -110
+    assert tp(17, 4, 0, 2) == -110
+    assert tp(4, 148, 0, 2) == -111
+    assert tp(4, 4, 2, 2) == -112
+    assert tp(4, 4, 0, 2, pads=vp(0)) == -113
+    assert tp(3, 4, 0, 2, n_tokens=1) == -114  # 1*2048 elements do not split into 3 chunks of whole 16-byte units
+    # a map handed to a build without expert parallelism
+    a, keep = _args(extra=[vp(0), p])
+    assert lib.launch_prefill_moe_wgmma_q1_ep(*a) == -121
+
+
+def test_expert_parallel_build_declines_without_map(built_libs):
+    lib = MonoKernel(built_libs["qwen_ep4"]).lib
+    a, keep = _args()
+    assert lib.launch_prefill_moe_wgmma_q1(*a) == -120          # the pre-existing ABI forwards a null map
+    a, keep = _args(extra=[ctypes.c_void_p(0), ctypes.c_void_p(0)])
+    assert lib.launch_prefill_moe_wgmma_q1_ep(*a) == -120
+
+
+def test_pad_words_and_caps(built_libs):
+    mk = MonoKernel(built_libs["ds_tp8"])
+    assert mk.tp_pad_words(8, 14, 8) == (8 * 14 + 1) * 8
+    caps = mk.tp_caps()
+    assert caps["usable"] and caps["has_tp_residual"] and caps["tp_max_c"] == 16 and caps["tp_mm"] == 8
+    assert caps["tp_has_devseq"] == 1 and caps["tp_seq_bytes"] == 4
+
+
+def test_loader_refuses_unset_binary(monkeypatch):
+    monkeypatch.delenv("VLLM_PREFILL_MONOKERNEL_SO", raising=False)
+    loader._reset_prefill_monokernel()
+    with pytest.raises(RuntimeError, match="VLLM_PREFILL_MONOKERNEL_SO is not set"):
+        loader.prefill_monokernel_geometry()
+    monkeypatch.setenv("VLLM_PREFILL_MONOKERNEL_SO", variant_path("qwen_tp4"))
+    loader._reset_prefill_monokernel()
+    assert loader.prefill_monokernel_geometry()["n_half"] == 128
+    loader._reset_prefill_monokernel()
+
+
+def test_validate_mirrors_reference_checks(built_libs):
+    mk = MonoKernel(built_libs["qwen_tp4"])
+    x = torch.zeros(4, 2048, dtype=torch.bfloat16)
+    w13 = torch.zeros(256, 256, 2048, dtype=torch.uint8)
+    w2 = torch.zeros(256, 2048, 128, dtype=torch.uint8)
+    assert mk.validate(x, w13, w2, 8, None) is None
+    with pytest.raises(RuntimeError, match="N_UP=256"):
+        mk.validate(x, torch.zeros(256, 512, 2048, dtype=torch.uint8), w2, 8, None)
+    with pytest.raises(RuntimeError, match="N_HALF=128"):
+        mk.validate(x, w13, torch.zeros(256, 2048, 256, dtype=torch.uint8), 8, None)
+    with pytest.raises(RuntimeError, match="K_DIM=2048"):
+        mk.validate(torch.zeros(4, 1024, dtype=torch.bfloat16), w13, w2, 8, None)
+    with pytest.raises(RuntimeError, match="local expert slabs"):
+        mk.validate(x, w13[:64], w2[:64], 8, None)
+    with pytest.raises(RuntimeError, match="TOP_K=8"):
+        mk.validate(x, w13, w2, 4, None)
+    with pytest.raises(RuntimeError, match="softmax"):
+        mk.validate(x, w13, w2, 8, torch.zeros(256))
+    with pytest.raises(RuntimeError, match="not EP capable"):
+        mk.validate(x, w13, w2, 8, None, torch.zeros(256, dtype=torch.int32))
+    ds = MonoKernel(built_libs["ds_tp8"])
+    xd = torch.zeros(4, 7168, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="sigmoid"):
+        ds.validate(xd, torch.zeros(256, 512, 7168, dtype=torch.uint8), torch.zeros(256, 7168, 256, dtype=torch.uint8), 8, None)
+    ep = MonoKernel(built_libs["qwen_ep4"])
+    w13e = torch.zeros(64, 1024, 2048, dtype=torch.uint8)
+    w2e = torch.zeros(64, 2048, 512, dtype=torch.uint8)
+    with pytest.raises(RuntimeError, match="no expert_map"):
+        ep.validate(x, w13e, w2e, 8, None)
+    with pytest.raises(RuntimeError, match="int32"):
+        ep.validate(x, w13e, w2e, 8, None, torch.zeros(256, dtype=torch.int64))
+    assert ep.validate(x, w13e, w2e, 8, None, synth.expert_map(synth.QWEN, 1, 4)) is None
+
+
+def test_no_cpu_fallback(built_libs):
+    mk = MonoKernel(built_libs["qwen_tp4"])
+    x = torch.zeros(4, 2048, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        mk.prefill(x, torch.zeros(4, 256), torch.zeros(256, 256, 2048, dtype=torch.uint8), torch.zeros(256, 2, 16),
+                   torch.zeros(256, 2048, 128, dtype=torch.uint8), torch.zeros(256, 16, 1))
+
+
+def test_synthetic_shards_are_slices_of_one_layer():
+    spec = synth.LayerSpec("t", hidden=256, inter=256, experts=8, top_k=2)
+    full = synth.make_layer(spec, seed=3, chunk=4, with_shared=False)
+    tp1 = synth.make_layer(spec, seed=3, chunk=4, with_shared=False, inter_slice=(128, 256))
+    assert torch.equal(tp1["w13"].view(torch.uint8)[:, :128], full["w13"].view(torch.uint8)[:, 128:256])
+    assert torch.equal(tp1["w13"].view(torch.uint8)[:, 128:], full["w13"].view(torch.uint8)[:, 384:512])
+    assert torch.equal(tp1["w2"].view(torch.uint8), full["w2"].view(torch.uint8)[:, :, 128:256])
+    assert torch.equal(tp1["w13_scale"], full["w13_scale"][:, [1, 3]])
+    assert torch.equal(tp1["w2_scale"], full["w2_scale"][:, :, 1:2])
+    ep1 = synth.make_layer(spec, seed=3, chunk=4, with_shared=False, expert_slice=(2, 6))
+    assert torch.equal(ep1["w13"].view(torch.uint8), full["w13"].view(torch.uint8)[2:6])
+    m = synth.expert_map(spec, 1, 2)
+    assert m.tolist() == [-1, -1, -1, -1, 0, 1, 2, 3]

@@ -1,0 +1,272 @@
+"""Parity of the CUDA kernel with the CPU oracle, through the C-ABI, on a B200.
+
+Bars: expert ids, per-expert counts/offsets and the sort permutation bit-exact; bf16 output
+max|err| <= 2e-2 * rms(ref) and cosine >= 0.9995 against the path-faithful oracle."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from unimonomoe_b200 import synth
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+@pytest.fixture(scope="module")
+def gu():
+    from tests import gpu_util
+    return gpu_util
+
+
+@pytest.fixture(scope="module")
+def qwen_full(built_libs):
+    from tests.gpu_util import DEV
+    return synth.make_layer(synth.QWEN, seed=0, device=DEV, with_shared=False)
+
+
+def tp_shard(full, rank, world, I=512):
+    lo, hi = rank * I // world, (rank + 1) * I // world
+    nb = I // 128
+    dev = full["w13"].device
+    rows = torch.cat([torch.arange(lo, hi), torch.arange(I + lo, I + hi)]).to(dev)
+    srows = torch.cat([torch.arange(lo // 128, hi // 128), torch.arange(nb + lo // 128, nb + hi // 128)]).to(dev)
+    return {"w13": full["w13"].view(torch.uint8)[:, rows].contiguous().view(torch.float8_e4m3fn),
+            "w13_scale": full["w13_scale"][:, srows].contiguous(),
+            "w2": full["w2"].view(torch.uint8)[:, :, lo:hi].contiguous().view(torch.float8_e4m3fn),
+            "w2_scale": full["w2_scale"][:, :, lo // 128:hi // 128].contiguous(), "bias": None,
+            "router_w": full["router_w"]}
+
+
+def ep_shard(full, rank, world):
+    n = 256 // world
+    sl = slice(rank * n, (rank + 1) * n)
+    return {k: (full[k][sl].contiguous() if k in ("w13", "w13_scale", "w2", "w2_scale") else full[k]) for k in full}
+
+
+@pytest.mark.parametrize("T", [1, 7, 256, 1000, 8192, 16384])
+def test_qwen_single_gpu_parity(gu, oracle, qwen_full, T):
+    mk = gu.kernel("qwen_w1")
+    batch = synth.make_batch(synth.QWEN, qwen_full, T, seed=0, device=gu.DEV)
+    res = gu.launch(mk, qwen_full, batch)
+    ids, w, _ = gu.check_routing(oracle, res, batch, 0, None, 256)
+    q, s = gu.check_act_quant(oracle, res, batch)
+    assert torch.isfinite(res["out"].float()).all()  # NaN-poisoned output fully overwritten
+    gu.check_output(oracle, res["out"], gu.sample_tokens(T, 48), q, s, ids, w, qwen_full)
+
+
+def test_run_to_run_bitwise_and_token_permutation(gu, oracle, qwen_full):
+    """Full-size property checks: two launches agree bit for bit, and permuting the tokens
+    permutes the output rows bit for bit (a row's arithmetic does not depend on its tile)."""
+    mk = gu.kernel("qwen_w1")
+    T = 16384
+    batch = synth.make_batch(synth.QWEN, qwen_full, T, seed=1, device=gu.DEV)
+    a = gu.launch(mk, qwen_full, batch)
+    out_a = a["out"].clone()
+    b = gu.launch(mk, qwen_full, batch)
+    assert torch.equal(out_a.view(torch.int16), b["out"].view(torch.int16))
+    assert (a["sorted"] == b["sorted"]).all()
+    srt = np.sort(a["sorted"])
+    assert (srt == np.arange(T * 8)).all() and a["counts"].sum() == T * 8
+    perm = torch.randperm(T, generator=torch.Generator().manual_seed(5)).to(gu.DEV)
+    pb = {"hs": batch["hs"][perm].contiguous(), "logits": batch["logits"][perm].contiguous()}
+    c = gu.launch(mk, qwen_full, pb)
+    assert torch.equal(c["out"].view(torch.int16), out_a[perm].view(torch.int16))
+
+
+def test_ragged_and_degenerate_routing(gu, oracle, qwen_full):
+    mk = gu.kernel("qwen_w1")
+    # skewed logits: ragged per-expert counts
+    batch = synth.make_batch(synth.QWEN, qwen_full, 3000, seed=2, device=gu.DEV, skew=1.0)
+    res = gu.launch(mk, qwen_full, batch)
+    ids, w, _ = gu.check_routing(oracle, res, batch, 0, None, 256)
+    q, s = gu.check_act_quant(oracle, res, batch)
+    assert res["counts"].max() > 4 * res["counts"].mean()
+    gu.check_output(oracle, res["out"], gu.sample_tokens(3000, 32, 1), q, s, ids, w, qwen_full)
+    # every token to the same eight experts: 248 empty experts, eight with T rows each
+    T = 1100
+    batch = synth.make_batch(synth.QWEN, qwen_full, T, seed=3, device=gu.DEV)
+    batch["logits"][:, [3, 40, 77, 100, 129, 200, 254, 255]] += 50.0
+    res = gu.launch(mk, qwen_full, batch)
+    ids, w, _ = gu.check_routing(oracle, res, batch, 0, None, 256)
+    assert (res["counts"] > 0).sum() == 8 and res["total_tiles"] == 8 * 9
+    gu.check_output(oracle, res["out"], gu.sample_tokens(T, 24, 2), *gu.check_act_quant(oracle, res, batch), ids, w, qwen_full)
+    # all-zero activations and constant logits: scales take the amax -> 1 branch, ties go to low ids
+    batch = {"hs": torch.zeros(130, 2048, dtype=torch.bfloat16, device=gu.DEV),
+             "logits": torch.zeros(130, 256, device=gu.DEV)}
+    res = gu.launch(mk, qwen_full, batch)
+    gu.check_routing(oracle, res, batch, 0, None, 256)
+    gu.check_act_quant(oracle, res, batch)
+    assert (res["ids"] == np.arange(8)[None]).all() and (res["out"].float() == 0).all()
+
+
+def test_golden_routing_through_the_kernel(gu, oracle, qwen_full, built_libs):
+    g = np.load(os.path.join(G, "routing.npz"))
+    logits = torch.from_numpy(g["logits"]).to(gu.DEV)
+    T = logits.shape[0]
+    hs = torch.randn(T, 2048, device=gu.DEV).to(torch.bfloat16)
+    res = gu.launch(gu.kernel("qwen_w1"), qwen_full, {"hs": hs, "logits": logits})
+    rows = np.setdiff1d(np.arange(T), g["tie_rows"])
+    assert (res["ids"][rows] == g["softmax_ids"][rows]).all()
+    assert np.allclose(res["weights"][rows], g["softmax_w"][rows], rtol=1e-5, atol=1e-8)
+    assert res["ids"][0].tolist() == list(range(8)) and res["ids"][1][:2].tolist() == [10, 200]
+
+
+def test_tensor_parallel_shards_sum_to_full(gu, oracle, qwen_full):
+    """Each TP=4 rank's kernel run in sequence on one GPU (validation/ep4_acc.py:5-9 does the
+    same for EP); the partial outputs must add up to the unsharded layer."""
+    T = 2048
+    batch = synth.make_batch(synth.QWEN, qwen_full, T, seed=4, device=gu.DEV)
+    mk = gu.kernel("qwen_tp4")
+    toks = gu.sample_tokens(T, 32, 3)
+    total = torch.zeros(T, 2048, device=gu.DEV)
+    ref_total = torch.zeros(len(toks), 2048)
+    for r in range(4):
+        sh = tp_shard(qwen_full, r, 4)
+        res = gu.launch(mk, sh, batch)
+        ids, w, _ = gu.check_routing(oracle, res, batch, 0, None, 256)
+        q, s = gu.check_act_quant(oracle, res, batch)
+        gu.check_output(oracle, res["out"], toks, q, s, ids, w, sh)
+        total += res["out"].float()
+        ref_total += oracle.moe_path(toks, q, s, ids, w, sh["w13"], sh["w13_scale"], sh["w2"], sh["w2_scale"]).float()
+    m = oracle.parity_metrics(total.cpu()[torch.from_numpy(toks).long()], ref_total)
+    assert m["max_abs_over_rms"] <= gu.MAX_ABS_OVER_RMS and m["cos"] >= gu.MIN_COS, m
+    full = gu.launch(gu.kernel("qwen_w1"), qwen_full, batch)
+    m2 = oracle.parity_metrics(total.cpu(), full["out"].float().cpu())
+    assert m2["cos"] > 0.999, m2
+
+
+def test_expert_parallel_ranks_in_sequence(gu, oracle, qwen_full):
+    """The reference's EP gates G1-G7 and G9 (validation/ep4_acc.py:338-391) with four ranks run in
+    sequence on one GPU."""
+    T = 2048
+    batch = synth.make_batch(synth.QWEN, qwen_full, T, seed=5, device=gu.DEV, skew=1.0)
+    mk = gu.kernel("qwen_ep4")
+    outs, tis, tws = [], [], []
+    q = s = None
+    for r in range(4):
+        emap = synth.expert_map(synth.QWEN, r, 4, device=gu.DEV)
+        sh = ep_shard(qwen_full, r, 4)
+        res = gu.launch(mk, sh, batch, expert_map=emap)                       # G1: rc == 0, status ok
+        ids, w, gids = gu.check_routing(oracle, res, batch, 0, None, 64, expert_map=emap)
+        q, s = gu.check_act_quant(oracle, res, batch)
+        assert res["ids"].min() >= -1 and res["ids"].max() < 64              # G2
+        assert torch.isfinite(res["out"].float()).all()                      # G6: poison fully overwritten
+        gu.check_output(oracle, res["out"], gu.sample_tokens(T, 16, r), q, s, ids, w, sh)
+        outs.append(res["out"].float()); tis.append(res["ids"]); tws.append(res["weights"])
+    owners = sum((t >= 0).astype(np.int32) for t in tis)
+    assert (owners == 1).all()                                               # G3
+    gti = np.full((T, 8), -1, np.int64)
+    for r in range(4):
+        gti = np.where(tis[r] >= 0, tis[r] + 64 * r, gti)
+    ref_ids = torch.topk(batch["logits"], 8, dim=1).indices.cpu().numpy()
+    assert (np.sort(gti, 1) == np.sort(ref_ids, 1)).all()                    # G4
+    for r in range(1, 4):
+        assert (tws[0].view(np.uint32) == tws[r].view(np.uint32)).all()      # G5
+    summed = torch.stack(outs).sum(0)
+    full = gu.launch(gu.kernel("qwen_w1"), qwen_full, batch)                 # G9: the full-width control
+    assert (np.sort(full["ids"], 1) == np.sort(gti, 1)).all()
+    assert (full["weights"].view(np.uint32) == tws[0].view(np.uint32)).all()
+    # the four partial outputs are each rounded to bf16 before they are added, the control is rounded
+    # once: the two agree to a few bf16 ulps, which is a looser bound than the one against the oracle
+    m = oracle.parity_metrics(summed.cpu(), full["out"].float().cpu())
+    assert m["rel_l2"] < 5e-3 and m["cos"] >= 0.99999, m
+    toks = gu.sample_tokens(T, 24, 9)
+    ref = oracle.moe_path(toks, q, s, full["ids"], full["weights"], qwen_full["w13"], qwen_full["w13_scale"],
+                          qwen_full["w2"], qwen_full["w2_scale"])
+    mp = oracle.parity_metrics(summed.cpu()[torch.from_numpy(toks).long()], ref.float())
+    assert mp["max_abs_over_rms"] <= gu.MAX_ABS_OVER_RMS and mp["cos"] >= gu.MIN_COS, mp
+    # G7, against the fp64 tier
+    ref64 = oracle.moe_fp64(batch["hs"].cpu()[torch.from_numpy(toks).long()], full["ids"][toks], full["weights"][toks],
+                            qwen_full["w13"].cpu(), qwen_full["w13_scale"].cpu(), qwen_full["w2"].cpu(),
+                            qwen_full["w2_scale"].cpu())
+    rl2, cs = oracle.rel_cos(summed.cpu()[torch.from_numpy(toks).long()], ref64)
+    assert rl2 < 6e-2 and cs > 0.998, (rl2, cs)
+
+
+@pytest.mark.parametrize("T", [256, 4096])
+def test_deepseek_tp8_shard_grouped_router(gu, oracle, T):
+    """DeepSeek-V3 geometry, one rank of TP=8 (H=7168, 256 of 2048 intermediate columns),
+    group-limited sigmoid router with bias."""
+    layer = synth.make_layer(synth.DEEPSEEK, seed=0, device=gu.DEV, inter_slice=(256, 512), with_shared=False, chunk=8)
+    batch = synth.make_batch(synth.DEEPSEEK, layer, T, seed=0, device=gu.DEV)
+    res = gu.launch(gu.kernel("ds_tp8"), layer, batch)
+    ids, w, _ = gu.check_routing(oracle, res, batch, 2, layer["bias"], 256)
+    q, s = gu.check_act_quant(oracle, res, batch)
+    assert torch.isfinite(res["out"].float()).all()
+    gu.check_output(oracle, res["out"], gu.sample_tokens(T, 12), q, s, ids, w, layer)
+    if T == 256:
+        g = np.load(os.path.join(G, "routing.npz"))
+        lg = torch.from_numpy(g["logits"]).to(gu.DEV)
+        gl = dict(layer, bias=torch.from_numpy(g["bias"]).to(gu.DEV))
+        hs = torch.randn(lg.shape[0], 7168, device=gu.DEV).to(torch.bfloat16)
+        r2 = gu.launch(gu.kernel("ds_tp8"), gl, {"hs": hs, "logits": lg})
+        rows = np.setdiff1d(np.arange(lg.shape[0]), g["tie_rows"])
+        assert (np.sort(r2["ids"], 1)[rows] == g["grouped_ids_sorted_fp32"][rows]).all()
+
+
+def test_folded_residual_and_output_scale(gu, oracle, qwen_full):
+    """The reference's fold gates (validation/tp8_fold_gate.py:332-409) on one GPU through the
+    _tp2 entry with the collective switched off: a null residual with scale 1 is bitwise inert,
+    scale 0 returns the residual, and out = bf16(2.5 * routed + residual)."""
+    mk = gu.kernel("qwen_w1")
+    T = 512
+    batch = synth.make_batch(synth.QWEN, qwen_full, T, seed=6, device=gu.DEV)
+    base = gu.launch(mk, qwen_full, batch)
+    resid = (torch.randn(T, 2048, device=gu.DEV) * 0.1).to(torch.bfloat16)
+    sc = mk.scratch(T, gu.DEV)
+    vp = ctypes.c_void_p
+
+    def tp2(residual, scale):
+        out = torch.full((T, 2048), float("nan"), dtype=torch.bfloat16, device=gu.DEV)
+        rc = mk.lib.launch_prefill_moe_wgmma_q1_tp2(
+            vp(batch["logits"].data_ptr()), T, 128, vp(sc["workspace"].data_ptr()), ctypes.c_size_t(sc["workspace"].numel()),
+            vp(batch["hs"].data_ptr()), vp(sc["act_fp8"].data_ptr()), vp(sc["act_scales"].data_ptr()),
+            vp(qwen_full["w13"].data_ptr()), vp(qwen_full["w13_scale"].data_ptr()), vp(qwen_full["w2"].data_ptr()),
+            vp(qwen_full["w2_scale"].data_ptr()), vp(sc["partial"].data_ptr()), vp(sc["topk_ids"].data_ptr()),
+            vp(sc["topk_weights"].data_ptr()), vp(sc["sorted_ids"].data_ptr()), vp(out.data_ptr()), vp(0),
+            vp(0), vp(0), 0, 1, 1, 0, ctypes.c_uint(0), vp(0),
+            vp(0 if residual is None else residual.data_ptr()), ctypes.c_float(scale),
+            vp(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0
+        mk.check_status(sc["workspace"])
+        return out
+
+    assert torch.equal(tp2(None, 1.0).view(torch.int16), base["out"].view(torch.int16))
+    assert torch.equal(tp2(resid, 0.0).view(torch.int16), resid.view(torch.int16))
+    folded = tp2(resid, 2.5)
+    q, s = gu.check_act_quant(oracle, base, batch)
+    toks = gu.sample_tokens(T, 24, 4)
+    gu.check_output(oracle, folded, toks, q, s, base["ids"], base["weights"], qwen_full, out_scale=2.5,
+                    residual=resid.cpu())
+
+
+def test_bounded_wait_reports_instead_of_hanging(gu, qwen_full):
+    """A rank barrier that no peer ever answers: the fused tensor-parallel epilogue is launched with
+    world = 2 while rank 1 does not exist (its barrier window is plain local memory that nothing
+    writes). The wait gives up after the time limit, the status word says which wait, and the
+    context stays usable: the next ordinary launch succeeds."""
+    mk = gu.kernel("qwen_w1")
+    T = 256
+    batch = synth.make_batch(synth.QWEN, qwen_full, T, seed=7, device=gu.DEV)
+    sc = mk.scratch(T, gu.DEV)
+    out = torch.zeros(T, 2048, dtype=torch.bfloat16, device=gu.DEV)
+    ncomm, nchunk, world = 4, 2, 2
+    pads = torch.zeros(world, mk.tp_pad_words(nchunk, ncomm, world), dtype=torch.int32, device=gu.DEV)
+    pad_ptrs = torch.tensor([pads[0].data_ptr(), pads[1].data_ptr()], dtype=torch.int64, device=gu.DEV)
+    seqctr = torch.zeros(1, dtype=torch.int32, device=gu.DEV)
+    mk.set_wait_timeout_us(200_000)
+    try:
+        with pytest.raises(RuntimeError, match="rank barrier timed out"):
+            # the "multicast" pointer is never dereferenced: the barrier in front of it fails first
+            mk.prefill_out(batch["hs"], batch["logits"], qwen_full["w13"], qwen_full["w13_scale"], qwen_full["w2"],
+                           qwen_full["w2_scale"], out, tp_mc_ptr=out.data_ptr(), tp_pads_ptr=pad_ptrs.data_ptr(),
+                           tp_seqctr_ptr=seqctr.data_ptr(), tp_rank=0, tp_world=world, tp_nchunk=nchunk,
+                           tp_ncomm=ncomm, check=True)
+    finally:
+        mk.set_wait_timeout_us(2_000_000)
+    assert int(seqctr.item()) == 1
+    res = gu.launch(mk, qwen_full, batch)
+    assert torch.isfinite(res["out"].float()).all()
