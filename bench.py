@@ -195,6 +195,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end leg, the library GEMM probe and the CPU baseline (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else max(args.warmup, 1)
     if args.impl == "reference":
@@ -275,7 +277,22 @@ def main() -> None:
     flops = synth.routed_flops(spec, T)  # whole job: all ranks together
     value = flops / (ms_per_step * 1e-3) / 1e12
 
-    # ---- end to end through the public API: host buffers in, host result out, copies inside the timed region
+    e2e_ms = None
+    if not args.kernel_only:
+        e2e_ms = time_e2e(args, mk, spec, layer, batch, out, emap, sc, world, dist, barrier, dev)
+    h2d = batch["hs"].numel() * 2 + batch["logits"].numel() * 4
+    d2h = out.numel() * 2
+
+    if rank == 0:
+        report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def time_e2e(args, mk, spec, layer, batch, out, emap, sc, world, dist, barrier, dev) -> float:
+    """End to end through the public API: host buffers in, host result out, copies inside the timed region."""
+    T = batch["hs"].shape[0]
     hs_host = batch["hs"].cpu().pin_memory()
     lg_host = batch["logits"].cpu().pin_memory()
     out_host = torch.empty(T, spec.hidden, dtype=torch.bfloat16).pin_memory()
@@ -303,13 +320,13 @@ def main() -> None:
     t = torch.tensor([e2.elapsed_time(e3) / n_e2e], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t[0])
-    h2d = hs_host.numel() * 2 + lg_host.numel() * 4
-    d2h = out_host.numel() * 2
+    return float(t[0])
 
-    if rank == 0:
+
+def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev) -> None:
+    if True:
         peaks = measured_peaks()
-        fp8_lib = fp8_gemm_tflops(dev) if world == 1 else None
+        fp8_lib = fp8_gemm_tflops(dev) if (world == 1 and not args.kernel_only) else None
         if peaks.get("bf16_tflops"):
             peak, peak_src = 2.0 * float(peaks["bf16_tflops"]), "2 x bf16_tflops (burst) of MEASURED_PEAKS.json: no fp8 figure is measured there"
         else:
@@ -331,20 +348,18 @@ def main() -> None:
                        "l2_policy": "inputs larger than L2: 805 MB of weights + 0.5 GB of partial rows stream per step",
                        "reduce": "none" if world == 1 else "NCCL all-reduce after the kernel"},
             "clocks": clk.summary(),
-            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "e2e": (None if e2e_ms is None else
+                    {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}),
             "gpu_launches": args.steps,
             "kernel_ms": kern_ms,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                          "traffic": traffic, "peak_source": peak_src, "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
                          "library_fp8_gemm_tflops": fp8_lib},
         }
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not args.kernel_only:
             line["cpu_baseline"] = time_cpu_baseline(spec, 256)
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

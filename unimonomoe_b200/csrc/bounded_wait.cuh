@@ -45,6 +45,7 @@ struct Workspace {
   uint32_t tp_seq_pub;                      // this launch's sequence number
   uint32_t reserved2;
   uint64_t phase_ns[8];                     // %globaltimer at phase boundaries, written by block 0
+  uint64_t prof[kGrid][16];                 // per-CTA stall counters (cycles), filled only by MONO_PROFILE builds
 };
 
 struct WaitCtx {

@@ -55,6 +55,18 @@
 #define MONO_ROUTER_MODE 0
 #endif
 
+#ifdef MONO_PROFILE
+#define PROF_DECL(n) long long n = 0
+#define PROF_T0() const long long prof_t0_ = clock64()
+#define PROF_ADD(n) n += clock64() - prof_t0_
+#define PROF_STORE(slot, n) p.ws->prof[blockIdx.x][slot] = static_cast<uint64_t>(n)
+#else
+#define PROF_DECL(n)
+#define PROF_T0()
+#define PROF_ADD(n)
+#define PROF_STORE(slot, n)
+#endif
+
 namespace mono {
 namespace {
 
@@ -74,7 +86,6 @@ constexpr int NK = K_DIM / 128;    // K slabs of the up projection
 constexpr int NP = N_HALF / 128;   // 128-column passes of the up projection = K slabs of the down projection
 constexpr int NHB = H_DIM / 256;   // 256-column passes of the down projection
 constexpr int TILE_M = 128;
-constexpr float BF16_MAX = 3.38953139e38f;
 
 static_assert(E == 256, "routing keeps 8 logits per lane: exactly 256 experts");
 static_assert(E_LOCAL > 0 && E_LOCAL <= E, "local experts are a subset");
@@ -98,14 +109,33 @@ constexpr int B_STAGE_BYTES = 256 * 128;     // 256 weight rows x 128 B
 constexpr int INTER_BYTES = NP * A_STAGE_BYTES;
 constexpr int SMEM_CAP = 227 * 1024;
 constexpr int SMEM_STATIC_RESERVE = 8 * 1024;
-constexpr int SMEM_AVAIL = SMEM_CAP - SMEM_STATIC_RESERVE - 1024 - INTER_BYTES;
+// per-tile scale staging: activation scales [NK][128], and (double buffered) the expert's
+// up-projection scales [2*NP*NK] and down-projection scales [(H/128)*NP]
+constexpr int WSU_N = 2 * NP * NK;
+constexpr int WSD_N = (H_DIM / 128) * NP;
+constexpr int SCALE_BYTES = ((NK * TILE_M + 2 * WSU_N + 2 * WSD_N) * 4 + 1023) / 1024 * 1024;
+constexpr int AS_PIECES = NK / 8;  // 16-byte pieces of activation scales each epilogue thread stages per tile
+static_assert(NK % 8 == 0, "each epilogue thread stages NK/2 activation scales in 16-byte pieces");
+static_assert(NHB >= AS_PIECES + 2, "the next tile's scales are staged during the down projection");
+constexpr int SMEM_AVAIL = SMEM_CAP - SMEM_STATIC_RESERVE - 1024 - INTER_BYTES - SCALE_BYTES;
 constexpr int SB_RAW = SMEM_AVAIL / (A_STAGE_BYTES + B_STAGE_BYTES);
 constexpr int SB = SB_RAW > 4 ? 4 : SB_RAW;
 constexpr int SA_RAW = (SMEM_AVAIL - SB * B_STAGE_BYTES) / A_STAGE_BYTES;
 constexpr int SA = SA_RAW > 4 ? 4 : SA_RAW;
 static_assert(SB >= 2 && SA >= 2, "intermediate too wide for shared memory: shard N_HALF further");
-constexpr int DYN_SMEM = 1024 + INTER_BYTES + SA * A_STAGE_BYTES + SB * B_STAGE_BYTES;
+constexpr int DYN_SMEM = 1024 + INTER_BYTES + SA * A_STAGE_BYTES + SB * B_STAGE_BYTES + SCALE_BYTES;
 static_assert(NWARPS * E * 4 <= SA * A_STAGE_BYTES + SB * B_STAGE_BYTES, "phase-0 histograms fit in the rings");
+
+// Register budget (setmaxnreg). The kernel launches with REGS_LAUNCH registers per thread; the
+// producer warpgroup gives registers back and the two epilogue warpgroups take them. The
+// hardware hands out only what this CTA released, and setmaxnreg.inc waits (without a bound)
+// until it is available, so the three counts MUST satisfy the inequality below.
+constexpr int REGS_LAUNCH = 168;    // 65536 / 384 rounded down to a multiple of 8
+constexpr int REGS_PRODUCER = 56;
+constexpr int REGS_EPILOGUE = 224;
+static_assert(128 * REGS_PRODUCER + N_EPI * REGS_EPILOGUE <= BLOCK * REGS_LAUNCH,
+              "setmaxnreg.inc would wait forever: the epilogue asks for more registers than the producers release");
+static_assert(REGS_LAUNCH * BLOCK <= 65536, "launch register count exceeds the register file");
 
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t IDESC = umma_idesc_e4m3_f32(128, 256);
@@ -194,12 +224,12 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
 // descending score order, ties to the lower expert id, weights renormalised by their sum
 // (clamped at 1e-30); modes 1/2 select on sigmoid+bias and weight by the unbiased sigmoid.
 // A slot for which no selectable expert remains gets id -1 and weight 0.
-__device__ __forceinline__ void route_token(const float* __restrict__ row, const float* __restrict__ bias,
-                                            int lane, int& my_id, float& my_w) {
+__device__ __forceinline__ void route_token(const float (&logit)[8], const float* __restrict__ bias, int lane,
+                                            int& my_id, float& my_w) {
   float sel[8], unb[8];
   float m = 0.f, s = 1.f;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) sel[j] = row[lane + 32 * j];
+  for (int j = 0; j < 8; ++j) sel[j] = logit[j];
   if constexpr (ROUTER_MODE == 0) {
     m = sel[0];
 #pragma unroll
@@ -296,7 +326,7 @@ __device__ __forceinline__ void route_token(const float* __restrict__ row, const
 __device__ __forceinline__ void quantize_activations(const Params& p, int gwarp, int nwarps, int lane) {
   const long long ngroups = static_cast<long long>(p.num_tokens) * NK;
   const int half = lane >> 4, sub = lane & 15;
-  constexpr int U = 4;
+  constexpr int U = 8;  // independent 16-byte loads in flight per lane
   for (long long g0 = static_cast<long long>(gwarp) * 2 + half; g0 < ngroups;
        g0 += static_cast<long long>(nwarps) * 2 * U) {
     uint4 raw[U];
@@ -377,6 +407,9 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
   uint8_t* inter = dyn;
   uint8_t* a_ring = dyn + INTER_BYTES;
   uint8_t* b_ring = a_ring + SA * A_STAGE_BYTES;
+  float* as_sm = reinterpret_cast<float*>(b_ring + SB * B_STAGE_BYTES);  // [NK][128]
+  float* wsu_sm = as_sm + NK * TILE_M;                                    // [2][WSU_N]
+  float* wsd_sm = wsu_sm + 2 * WSU_N;                                     // [2][WSD_N]
   int* hist = reinterpret_cast<int*>(a_ring);  // [NWARPS][E], phases 0-1 only
 
   if (bid == 0 && tid == 0) ws->phase_ns[0] = globaltimer_ns();
@@ -400,10 +433,22 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
   const int t_begin = min(T, gwarp * tok_per_warp);
   const int t_end = min(T, t_begin + tok_per_warp);
 
+  float lg_next[8];
+  if (t_begin < t_end) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) lg_next[j] = p.logits[static_cast<size_t>(t_begin) * E + lane + 32 * j];
+  }
   for (int t = t_begin; t < t_end; ++t) {
     int my_id;
     float my_w;
-    route_token(p.logits + static_cast<size_t>(t) * E, p.router_bias, lane, my_id, my_w);
+    float lg[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) lg[j] = lg_next[j];
+    if (t + 1 < t_end) {  // the next token's logits are in flight while this one is routed
+#pragma unroll
+      for (int j = 0; j < 8; ++j) lg_next[j] = p.logits[static_cast<size_t>(t + 1) * E + lane + 32 * j];
+    }
+    route_token(lg, p.router_bias, lane, my_id, my_w);
     if (lane < TOP_K) {
       int lid = my_id;
       if constexpr (EP_BUILD) lid = (my_id >= 0) ? p.expert_map[my_id] : -1;
@@ -524,8 +569,8 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
   if (tid == 0) {
     for (int s = 0; s < SA; ++s) { mbar_init(&S.fullA[s], N_GATHER); mbar_init(&S.emptyA[s], 1); }
     for (int s = 0; s < SB; ++s) { mbar_init(&S.fullB[s], 1); mbar_init(&S.emptyB[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&S.tmem_full[s], 1); mbar_init(&S.tmem_empty[s], N_EPI); }
-    mbar_init(&S.inter_ready, N_EPI);
+    for (int s = 0; s < 2; ++s) { mbar_init(&S.tmem_full[s], 1); mbar_init(&S.tmem_empty[s], N_EPI / 32); }
+    mbar_init(&S.inter_ready, N_EPI / 32);
     mbar_init_fence();
   }
   if (warp == WARP_MMA) {
@@ -539,6 +584,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
   const int n_my = alive ? S.n_my_tiles : 0;
 
   if (warp < 4) {
+    reg_dec<REGS_PRODUCER>();
     if (warp == WARP_TMA) {
       // ---------------------------------------------------------- weight producer
       if (lane == 0) {
@@ -546,6 +592,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         tma_prefetch_desc(&p.tm_down);
         uint32_t nb = 0;
         bool ok = true;
+        PROF_DECL(pw_emptyB);
         for (int it = 0; it < n_my && ok; ++it) {
           const int e = S.tiles[it].e;
           for (int ps = 0; ps < NP && ok; ++ps) {
@@ -553,7 +600,9 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             const uint32_t yu = yg + N_HALF;
             for (int ks = 0; ks < NK; ++ks) {
               const uint32_t st = nb % SB, ph = (nb / SB) & 1u;
+              { PROF_T0();
               if (!mbar_wait(&S.emptyB[st], ph ^ 1u, wc, kSiteEmptyB)) { ok = false; break; }
+              PROF_ADD(pw_emptyB); }
               mbar_arrive_expect_tx(&S.fullB[st], B_STAGE_BYTES);
               uint8_t* dst = b_ring + st * B_STAGE_BYTES;
               const uint32_t x = static_cast<uint32_t>(ks * 128);
@@ -581,19 +630,30 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             }
           }
         }
+        PROF_STORE(0, pw_emptyB);
       }
     } else if (warp == WARP_MMA) {
       // ---------------------------------------------------------- MMA issuer
       if (lane == 0) {
         uint32_t nb = 0, na = 0, nt = 0;
         bool ok = true;
+        PROF_DECL(pm_fullB); PROF_DECL(pm_fullA); PROF_DECL(pm_tmem); PROF_DECL(pm_inter); PROF_DECL(pm_total);
+#ifdef MONO_PROFILE
+        const long long pm_start = clock64();
+#endif
         const uint32_t a_ring_u32 = smem_u32(a_ring), b_ring_u32 = smem_u32(b_ring), inter_u32 = smem_u32(inter);
         for (int it = 0; it < n_my && ok; ++it) {
           for (int s = 0; s < NP * NK; ++s) {
             const uint32_t sb = nb % SB, sa = na % SA, buf = nt & 1u;
+            { PROF_T0();
             if (!mbar_wait(&S.fullB[sb], (nb / SB) & 1u, wc, kSiteFullB)) { ok = false; break; }
+            PROF_ADD(pm_fullB); }
+            { PROF_T0();
             if (!mbar_wait(&S.fullA[sa], (na / SA) & 1u, wc, kSiteFullA)) { ok = false; break; }
+            PROF_ADD(pm_fullA); }
+            { PROF_T0();
             if (!mbar_wait(&S.tmem_empty[buf], ((nt >> 1) & 1u) ^ 1u, wc, kSiteTmemEmpty)) { ok = false; break; }
+            PROF_ADD(pm_tmem); }
             tc_fence_after();
             const uint64_t da = umma_desc_sw128(a_ring_u32 + sa * A_STAGE_BYTES);
             const uint64_t db = umma_desc_sw128(b_ring_u32 + sb * B_STAGE_BYTES);
@@ -606,13 +666,19 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             ++nb; ++na; ++nt;
           }
           if (!ok) break;
+          { PROF_T0();
           if (!mbar_wait(&S.inter_ready, static_cast<uint32_t>(it) & 1u, wc, kSiteInterReady)) { ok = false; break; }
+          PROF_ADD(pm_inter); }
           tc_fence_after();
           for (int s = 0; s < NHB * NP; ++s) {
             const int dk = s % NP;
             const uint32_t sb = nb % SB, buf = nt & 1u;
+            { PROF_T0();
             if (!mbar_wait(&S.fullB[sb], (nb / SB) & 1u, wc, kSiteFullB)) { ok = false; break; }
+            PROF_ADD(pm_fullB); }
+            { PROF_T0();
             if (!mbar_wait(&S.tmem_empty[buf], ((nt >> 1) & 1u) ^ 1u, wc, kSiteTmemEmpty)) { ok = false; break; }
+            PROF_ADD(pm_tmem); }
             tc_fence_after();
             const uint64_t da = umma_desc_sw128(inter_u32 + dk * A_STAGE_BYTES);
             const uint64_t db = umma_desc_sw128(b_ring_u32 + sb * B_STAGE_BYTES);
@@ -624,12 +690,18 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             ++nb; ++nt;
           }
         }
+#ifdef MONO_PROFILE
+        pm_total = clock64() - pm_start;
+#endif
+        PROF_STORE(1, pm_fullB); PROF_STORE(2, pm_fullA); PROF_STORE(3, pm_tmem); PROF_STORE(4, pm_inter);
+        PROF_STORE(5, pm_total);
       }
     } else {
       // ---------------------------------------------------------- activation gather (64 threads)
       const int gt = tid - WARP_GATHER0 * 32;
       uint32_t na = 0;
       bool ok = true;
+      PROF_DECL(pg_emptyA); PROF_DECL(pg_cpwait);
       const uint32_t a_ring_u32 = smem_u32(a_ring);
       for (int it = 0; it < n_my && ok; ++it) {
         const TileInfo ti = S.tiles[it];
@@ -646,11 +718,12 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
 #pragma unroll
           for (int c = 0; c < 8; ++c) off[h][c] = sw128(r, c);
         }
-        int prev = -1;
         for (int s = 0; s < NP * NK; ++s) {
           const int ks = s % NK;
           const uint32_t sa = na % SA;
+          { PROF_T0();
           if (!mbar_wait(&S.emptyA[sa], ((na / SA) & 1u) ^ 1u, wc, kSiteEmptyA)) { ok = false; break; }
+          PROF_ADD(pg_emptyA); }
           const uint32_t dst = a_ring_u32 + sa * A_STAGE_BYTES;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
@@ -660,26 +733,20 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               for (int c = 0; c < 8; ++c) cp_async16(dst + off[h][c], g + c * 16);
             }
           }
-          cp_async_commit();
-          if (prev >= 0) {
-            cp_async_wait<1>();
-            fence_proxy_async_smem();
-            mbar_arrive(&S.fullA[prev]);
-          }
-          prev = static_cast<int>(sa);
+          // the barrier receives this thread's arrival when the copies above have landed
+          cp_async_arrive_noinc(&S.fullA[sa]);
           ++na;
         }
-        cp_async_wait<0>();
-        if (ok && prev >= 0) {
-          fence_proxy_async_smem();
-          mbar_arrive(&S.fullA[prev]);
-        }
       }
+      cp_async_commit();
       cp_async_wait<0>();
+      if (gt == 0) { PROF_STORE(6, pg_emptyA); PROF_STORE(7, pg_cpwait); }
     }
     __syncwarp();
+    reg_inc<REGS_LAUNCH>();
   } else {
     // ------------------------------------------------------------ epilogue (256 threads)
+    reg_inc<REGS_EPILOGUE>();
     {
       const int et = tid - 128;
       const int h = et >> 7;               // which 128 TMEM columns of the 256-column buffer
@@ -688,70 +755,128 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(h * 128);
       uint32_t nt = 0;
       bool dead = false;  // after an abort: keep the loop structure (named barriers stay matched), skip the work
-      float acc[128];
+      float2 acc[64];     // pairs of adjacent columns; [0,32) gate (or down cols 0..63), [32,64) up (down cols 64..127)
+      PROF_DECL(pe_bar); PROF_DECL(pe_zero); PROF_DECL(pe_wait); PROF_DECL(pe_up); PROF_DECL(pe_silu); PROF_DECL(pe_down); PROF_DECL(pe_store);
+#ifdef MONO_PROFILE
+      const long long pe_start = clock64();
+#endif
+
+      // one 128-deep K slab: acc += D * scale, 64 TMEM columns per load, packed fp32x2 FMAs
+      auto promote = [&](uint32_t buf, float s_lo, float s_hi) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[64];
+          tmem_ld64(t_lane + buf * 256u + c * 64u, v);
+          tmem_ld_wait();
+          const float sc = (c == 0) ? s_lo : s_hi;
+          const float2 s2 = make_float2(sc, sc);
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            acc[c * 32 + j] = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])), s2,
+                                         acc[c * 32 + j]);
+        }
+        // one arrival per warp: 256 per-thread arrivals on one shared-memory word serialise
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&S.tmem_empty[buf]);
+      };
+
+      // Scales are staged in shared memory one tile ahead: nothing in the slab loop waits on a
+      // global load. stage_* below fetch tile `nx`: its row's slot id, routing weight and
+      // activation scales, and the expert's weight scales (into buffer nx & 1).
+      int nfi = -1;
+      float nrw = 0.f, wsu_v = 0.f, wsd_v = 0.f;
+      float4 as_v = make_float4(0.f, 0.f, 0.f, 0.f);
+      auto stage_ids = [&](int nx) {
+        const TileInfo tn = S.tiles[nx];
+        nfi = -1;
+        if (r < tn.rows) {
+          nfi = __ldcg(&p.sorted_ids[tn.row0 + r]);
+          if (nfi < 0 || nfi >= numel) nfi = -1;
+        }
+        if (et < WSU_N) wsu_v = __ldg(p.up_w_scales + static_cast<size_t>(tn.e) * WSU_N + et);
+        if (et < WSD_N) wsd_v = __ldg(p.down_w_scales + static_cast<size_t>(tn.e) * WSD_N + et);
+      };
+      auto stage_weight_store = [&](int nx) {
+        nrw = (nfi >= 0) ? __ldcg(&p.topk_weights[nfi]) : 0.f;
+        if (et < WSU_N) wsu_sm[(nx & 1) * WSU_N + et] = wsu_v;
+        if (et < WSD_N) wsd_sm[(nx & 1) * WSD_N + et] = wsd_v;
+        if constexpr (WSU_N > N_EPI) {
+          for (int i = et + N_EPI; i < WSU_N; i += N_EPI)
+            wsu_sm[(nx & 1) * WSU_N + i] = __ldg(p.up_w_scales + static_cast<size_t>(S.tiles[nx].e) * WSU_N + i);
+        }
+        if constexpr (WSD_N > N_EPI) {
+          for (int i = et + N_EPI; i < WSD_N; i += N_EPI)
+            wsd_sm[(nx & 1) * WSD_N + i] = __ldg(p.down_w_scales + static_cast<size_t>(S.tiles[nx].e) * WSD_N + i);
+        }
+      };
+      auto as_piece_load = [&](int j) {
+        as_v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (nfi >= 0)
+          as_v = __ldcg(reinterpret_cast<const float4*>(p.act_scales + static_cast<size_t>(nfi / TOP_K) * NK + h * (NK / 2) + 4 * j));
+      };
+      auto as_piece_store = [&](int j) {
+        float* d = as_sm + (h * (NK / 2) + 4 * j) * TILE_M + r;
+        d[0] = as_v.x; d[TILE_M] = as_v.y; d[2 * TILE_M] = as_v.z; d[3 * TILE_M] = as_v.w;
+      };
+      if (n_my > 0) {
+        stage_ids(0);
+        stage_weight_store(0);
+        for (int j = 0; j < AS_PIECES; ++j) { as_piece_load(j); as_piece_store(j); }
+      }
 
       for (int it = 0; it < n_my; ++it) {
         const TileInfo ti = S.tiles[it];
-        const int e = ti.e;
-        int fi = -1;
-        if (r < ti.rows) {
-          fi = __ldcg(&p.sorted_ids[ti.row0 + r]);
-          if (fi < 0 || fi >= numel) fi = -1;
-        }
-        const float rw = (fi >= 0) ? __ldcg(&p.topk_weights[fi]) : 0.f;
-        const float* as_row = (fi >= 0) ? (p.act_scales + static_cast<size_t>(fi / TOP_K) * NK) : nullptr;
+        const int fi = nfi;
+        const float rw = nrw;
+        const float2 rw2 = make_float2(rw, rw);
+        const float* wsu_t = wsu_sm + (it & 1) * WSU_N;
+        const float* wsd_t = wsd_sm + (it & 1) * WSD_N + h * NP;
+        const bool has_next = it + 1 < n_my;
         float iscale[NP];
+        { PROF_T0();
+        named_bar_sync(1, N_EPI);  // this tile's staged scales are visible to all epilogue threads
+        PROF_ADD(pe_bar); }
 
         // ---------------- up projection + SiLU*mul + requantisation
         for (int ps = 0; ps < NP; ++ps) {
+          { PROF_T0();
 #pragma unroll
-          for (int i = 0; i < 128; ++i) acc[i] = 0.f;
-          const float* wsg_p = p.up_w_scales + (static_cast<size_t>(e) * (2 * NP) + ps) * NK;
-          const float* wsu_p = wsg_p + static_cast<size_t>(NP) * NK;
-          float as_n = as_row ? __ldcg(as_row) : 0.f;
-          float wg_n = __ldg(wsg_p), wu_n = __ldg(wsu_p);
+          for (int i = 0; i < 64; ++i) acc[i] = make_float2(0.f, 0.f);
+          PROF_ADD(pe_zero); }
           for (int ks = 0; ks < NK; ++ks) {
-            const float a_s = as_n, w_g = wg_n, w_u = wu_n;
-            if (ks + 1 < NK) {
-              as_n = as_row ? __ldcg(as_row + ks + 1) : 0.f;
-              wg_n = __ldg(wsg_p + ks + 1);
-              wu_n = __ldg(wsu_p + ks + 1);
-            }
+            const float a_s = as_sm[ks * TILE_M + r];
+            const float w_g = wsu_t[ps * NK + ks], w_u = wsu_t[(NP + ps) * NK + ks];
             const uint32_t buf = nt & 1u;
+            { PROF_T0();
             if (!dead && !mbar_wait(&S.tmem_full[buf], (nt >> 1) & 1u, wc, kSiteTmemFull)) dead = true;
-            if (!dead) {
-              tc_fence_after();
-              const float sg = __fmul_rn(w_g, a_s), su = __fmul_rn(w_u, a_s);
-#pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld32(t_lane + buf * 256u + c * 32u, v);
-                tmem_ld_wait();
-                const float sc = (c < 2) ? sg : su;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __fmaf_rn(__uint_as_float(v[j]), sc, acc[c * 32 + j]);
-              }
-              tc_fence_before();
-              mbar_arrive(&S.tmem_empty[buf]);
-            }
+            PROF_ADD(pe_wait); }
+            PROF_T0();
+            if (!dead) promote(buf, __fmul_rn(w_g, a_s), __fmul_rn(w_u, a_s));
+            PROF_ADD(pe_up);
             ++nt;
           }
+          PROF_T0();
           if (p.dbg_acc != nullptr && fi >= 0 && !dead) {
             float* d = p.dbg_acc + static_cast<size_t>(ti.row0 + r) * N_UP;
 #pragma unroll
-            for (int j = 0; j < 64; ++j) {
-              d[ps * 128 + h * 64 + j] = acc[j];
-              d[N_HALF + ps * 128 + h * 64 + j] = acc[64 + j];
+            for (int j = 0; j < 32; ++j) {
+              d[ps * 128 + h * 64 + 2 * j] = acc[j].x;
+              d[ps * 128 + h * 64 + 2 * j + 1] = acc[j].y;
+              d[N_HALF + ps * 128 + h * 64 + 2 * j] = acc[32 + j].x;
+              d[N_HALF + ps * 128 + h * 64 + 2 * j + 1] = acc[32 + j].y;
             }
           }
-          // SiLU(gate) * up, written over the gate half of the accumulators
+          // SiLU(gate) * up (kernel/qwen_tp/src/prefill_mono_final_nb.cu:678), written over the gate half
           float mx = 0.f;
 #pragma unroll
-          for (int j = 0; j < 64; ++j) {
-            const float g = acc[j];
-            const float v = __fdividef(acc[64 + j] * g, 1.0f + __expf(-g));
-            acc[j] = v;
-            mx = fmaxf(mx, fabsf(v));
+          for (int j = 0; j < 32; ++j) {
+            const float g0 = acc[j].x, g1 = acc[j].y;
+            const float v0 = __fdividef(acc[32 + j].x * g0, 1.0f + __expf(-g0));
+            const float v1 = __fdividef(acc[32 + j].y * g1, 1.0f + __expf(-g1));
+            acc[j] = make_float2(v0, v1);
+            mx = fmaxf(mx, fmaxf(fabsf(v0), fabsf(v1)));
           }
           S.rowmax[ps & 1][h][r] = mx;
           named_bar_sync(1, N_EPI);
@@ -766,66 +891,77 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint4 qv;
-            qv.x = pack_e4m3x4(acc[c * 16 + 0] * inv, acc[c * 16 + 1] * inv, acc[c * 16 + 2] * inv, acc[c * 16 + 3] * inv);
-            qv.y = pack_e4m3x4(acc[c * 16 + 4] * inv, acc[c * 16 + 5] * inv, acc[c * 16 + 6] * inv, acc[c * 16 + 7] * inv);
-            qv.z = pack_e4m3x4(acc[c * 16 + 8] * inv, acc[c * 16 + 9] * inv, acc[c * 16 + 10] * inv, acc[c * 16 + 11] * inv);
-            qv.w = pack_e4m3x4(acc[c * 16 + 12] * inv, acc[c * 16 + 13] * inv, acc[c * 16 + 14] * inv, acc[c * 16 + 15] * inv);
+            qv.x = pack_e4m3x4(acc[c * 8 + 0].x * inv, acc[c * 8 + 0].y * inv, acc[c * 8 + 1].x * inv, acc[c * 8 + 1].y * inv);
+            qv.y = pack_e4m3x4(acc[c * 8 + 2].x * inv, acc[c * 8 + 2].y * inv, acc[c * 8 + 3].x * inv, acc[c * 8 + 3].y * inv);
+            qv.z = pack_e4m3x4(acc[c * 8 + 4].x * inv, acc[c * 8 + 4].y * inv, acc[c * 8 + 5].x * inv, acc[c * 8 + 5].y * inv);
+            qv.w = pack_e4m3x4(acc[c * 8 + 6].x * inv, acc[c * 8 + 6].y * inv, acc[c * 8 + 7].x * inv, acc[c * 8 + 7].y * inv);
             *reinterpret_cast<uint4*>(irow + sw128(r, h * 4 + c)) = qv;
             if (p.dbg_inter != nullptr && fi >= 0 && !dead)
               *reinterpret_cast<uint4*>(p.dbg_inter + static_cast<size_t>(ti.row0 + r) * N_HALF + ps * 128 + h * 64 + c * 16) = qv;
           }
           if (p.dbg_inter_scale != nullptr && fi >= 0 && h == 0 && !dead)
             p.dbg_inter_scale[static_cast<size_t>(ti.row0 + r) * NP + ps] = my_scale;
+          PROF_ADD(pe_silu);
         }
         // publish the intermediate to the tensor core (async proxy) and release the MMA thread
         fence_proxy_async_smem();
-        mbar_arrive(&S.inter_ready);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&S.inter_ready);
 
-        // ---------------- down projection, routing weight, bf16 partial rows
+        // ---------------- down projection, routing weight, bf16 partial rows.
+        // Every epilogue thread is past the last pass's barrier, so nobody reads this tile's
+        // activation scales any more: the next tile's are staged while the down slabs run.
+        if (has_next) stage_ids(it + 1);
         for (int hb = 0; hb < NHB; ++hb) {
 #pragma unroll
-          for (int i = 0; i < 128; ++i) acc[i] = 0.f;
-          const float* dws_p = p.down_w_scales + (static_cast<size_t>(e) * (H_DIM / 128) + hb * 2 + h) * NP;
+          for (int i = 0; i < 64; ++i) acc[i] = make_float2(0.f, 0.f);
+          if (has_next) {
+            if (hb == 1) stage_weight_store(it + 1);
+            if (hb >= 1 && hb - 1 < AS_PIECES) as_piece_load(hb - 1);
+          }
 #pragma unroll
           for (int dk = 0; dk < NP; ++dk) {
-            const float sc = __fmul_rn(__ldg(dws_p + dk), iscale[dk]);
+            const float sc = __fmul_rn(wsd_t[hb * 2 * NP + dk], iscale[dk]);
             const uint32_t buf = nt & 1u;
+            { PROF_T0();
             if (!dead && !mbar_wait(&S.tmem_full[buf], (nt >> 1) & 1u, wc, kSiteTmemFull)) dead = true;
-            if (!dead) {
-              tc_fence_after();
-#pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld32(t_lane + buf * 256u + c * 32u, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __fmaf_rn(__uint_as_float(v[j]), sc, acc[c * 32 + j]);
-              }
-              tc_fence_before();
-              mbar_arrive(&S.tmem_empty[buf]);
-            }
+            PROF_ADD(pe_wait); }
+            PROF_T0();
+            if (!dead) promote(buf, sc, sc);
+            PROF_ADD(pe_down);
             ++nt;
           }
+          PROF_T0();
           if (fi >= 0 && !dead) {
             __nv_bfloat16* dst = p.partial + static_cast<size_t>(fi) * H_DIM + hb * 256 + h * 128;
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              uint32_t w[4];
+            for (int c = 0; c < 8; ++c) {  // 16 bf16 = 32 bytes per store: whole sectors
+              uint32_t w[8];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float v0 = acc[c * 8 + 2 * j] * rw, v1 = acc[c * 8 + 2 * j + 1] * rw;
-                v0 = fminf(fmaxf(v0, -BF16_MAX), BF16_MAX);
-                v1 = fminf(fmaxf(v1, -BF16_MAX), BF16_MAX);
-                const __nv_bfloat162 b2 = __floats2bfloat162_rn(v0, v1);
-                w[j] = *reinterpret_cast<const uint32_t*>(&b2);
+              for (int j = 0; j < 8; ++j) {
+                // times the routing weight, then bf16 with saturation to the largest finite value
+                // (the clamp of kernel/qwen_tp/src/prefill_mono_final_nb.cu:916)
+                const float2 v = __fmul2_rn(acc[c * 8 + j], rw2);
+                w[j] = cvt_bf16x2_satfinite(v.x, v.y);
               }
-              *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+              st_global_256(dst + c * 16, w);
             }
           }
+          if (has_next && hb >= 1 && hb - 1 < AS_PIECES) as_piece_store(hb - 1);
+          PROF_ADD(pe_store);
         }
       }
+      if (et == 0) {
+        PROF_STORE(8, pe_wait); PROF_STORE(9, pe_up); PROF_STORE(10, pe_silu); PROF_STORE(11, pe_down);
+        PROF_STORE(12, pe_store); PROF_STORE(14, pe_bar); PROF_STORE(15, pe_zero);
+#ifdef MONO_PROFILE
+        p.ws->prof[blockIdx.x][13] = static_cast<uint64_t>(clock64() - pe_start);
+#endif
+      }
     }
+    reg_dec<REGS_LAUNCH>();
   }
+
 
   // teardown of phase 2: when aborting, give in-flight bulk copies and MMAs time to land
   if (aborted(ws)) __nanosleep(200000);
@@ -1067,6 +1203,7 @@ int prefill_wgmma_counts_offset() { return static_cast<int>(offsetof(Workspace, 
 int prefill_wgmma_offsets_offset() { return static_cast<int>(offsetof(Workspace, expert_offsets)); }
 int prefill_wgmma_total_tiles_offset() { return static_cast<int>(offsetof(Workspace, total_tiles)); }
 int prefill_wgmma_phase_ns_offset() { return static_cast<int>(offsetof(Workspace, phase_ns)); }
+int prefill_wgmma_prof_offset() { return static_cast<int>(offsetof(Workspace, prof)); }
 // Upper bound, in microseconds, of every device-side wait of later launches.
 void prefill_wgmma_set_wait_timeout_us(unsigned long long us) { g_timeout_ns = us * 1000ull; }
 // Debug dump targets for later launches (device pointers, or null to switch off):
