@@ -55,6 +55,14 @@
 #define MONO_ROUTER_MODE 0
 #endif
 
+// Development only: MONO_ABLATE is a bit mask that removes a piece of the epilogue's work (the
+// results are then wrong) so that its share of the run time can be measured by difference.
+//   1: no TMEM read-out / promotion   2: no SiLU / requantisation arithmetic   4: no partial-row stores
+//   8: no activation gather copies    16: no weight TMA loads
+#ifndef MONO_ABLATE
+#define MONO_ABLATE 0
+#endif
+
 #ifdef MONO_PROFILE
 #define PROF_DECL(n) long long n = 0
 #define PROF_T0() const long long prof_t0_ = clock64()
@@ -95,11 +103,38 @@ static_assert(NK % 2 == 0, "activation quantisation pairs two 128-column groups 
 static_assert(ROUTER_MODE != 2 || N_GROUP * 32 == E, "grouped routing assumes 32 experts per group");
 
 // ------------------------------------------------------------------ launch shape
-constexpr int BLOCK = 384;
+// Warps 0-3 are the producer warpgroup (weight TMA, MMA issue, two gather warps); the epilogue is
+// EPI_WGS warpgroups of 128 threads. Thread i of an epilogue warpgroup owns row i of the tile
+// (TMEM lane i); warpgroup h owns columns [h*WC, (h+1)*WC) of every accumulator buffer: HCB gate
+// columns followed by the HCB matching up columns in the up projection, WC output columns in
+// the down projection.
+#ifndef MONO_EPI_WGS
+#define MONO_EPI_WGS 2
+#endif
+#ifndef MONO_NSPLIT
+#define MONO_NSPLIT 1
+#endif
+constexpr int EPI_WGS = MONO_EPI_WGS;
+static_assert(EPI_WGS == 2 || EPI_WGS == 4, "two or four epilogue warpgroups");
+// A 128-deep K slab of the 256 weight rows of a stage is issued as NSPLIT independent MMAs of
+// N = BC columns, each into its own TMEM buffer, so the epilogue's read-out of one buffer is a
+// single short dependency chain and the MMA thread can run NBUF-1 buffers ahead of it.
+constexpr int NSPLIT = MONO_NSPLIT;
+constexpr int BC = 256 / NSPLIT;         // columns of one accumulator buffer = N of one MMA
+constexpr int NBUF = 2 * NSPLIT;         // accumulator buffers in tensor memory (512 columns in all)
+constexpr int WC = BC / EPI_WGS;         // columns of one buffer owned by one epilogue warpgroup
+constexpr int HCB = WC / 2;              // gate (= up) columns per warpgroup per buffer
+constexpr int TCOLS = NSPLIT * WC;       // accumulator columns (fp32 registers) per epilogue thread
+constexpr int PASS_STRIDE = 128 / NSPLIT;  // intermediate columns covered by one buffer in the up projection
+constexpr int LDW = (WC <= 64) ? WC : HCB;  // TMEM columns per tcgen05.ld
+constexpr int NLD = WC / LDW;
+static_assert(HCB == 32 || HCB == 64, "unsupported split of the accumulator between warpgroups");
+static_assert(LDW == 32 || LDW == 64, "TMEM loads are 32 or 64 columns wide");
+constexpr int N_EPI = EPI_WGS * 128;
+constexpr int BLOCK = 128 + N_EPI;
 constexpr int NWARPS = BLOCK / 32;
-constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_GATHER0 = 2;  // warps 2,3 gather; warps 4..11 epilogue
+constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_GATHER0 = 2;  // warps 2,3 gather; warps 4.. epilogue
 constexpr int N_GATHER = 64;
-constexpr int N_EPI = 256;
 constexpr int MAX_MY_TILES = 32;
 constexpr int MAX_TILES = MAX_MY_TILES * kGrid;
 
@@ -108,7 +143,7 @@ constexpr int A_STAGE_BYTES = TILE_M * 128;  // 128 rows x 128 B
 constexpr int B_STAGE_BYTES = 256 * 128;     // 256 weight rows x 128 B
 constexpr int INTER_BYTES = NP * A_STAGE_BYTES;
 constexpr int SMEM_CAP = 227 * 1024;
-constexpr int SMEM_STATIC_RESERVE = 8 * 1024;
+constexpr int SMEM_STATIC_RESERVE = 6 * 1024;
 // per-tile scale staging: activation scales [NK][128], and (double buffered) the expert's
 // up-projection scales [2*NP*NK] and down-projection scales [(H/128)*NP]
 constexpr int WSU_N = 2 * NP * NK;
@@ -124,21 +159,21 @@ constexpr int SA_RAW = (SMEM_AVAIL - SB * B_STAGE_BYTES) / A_STAGE_BYTES;
 constexpr int SA = SA_RAW > 4 ? 4 : SA_RAW;
 static_assert(SB >= 2 && SA >= 2, "intermediate too wide for shared memory: shard N_HALF further");
 constexpr int DYN_SMEM = 1024 + INTER_BYTES + SA * A_STAGE_BYTES + SB * B_STAGE_BYTES + SCALE_BYTES;
-static_assert(NWARPS * E * 4 <= SA * A_STAGE_BYTES + SB * B_STAGE_BYTES, "phase-0 histograms fit in the rings");
+static_assert(NWARPS * E * 4 <= SA * A_STAGE_BYTES, "phase-0 histograms live in the activation ring");
 
 // Register budget (setmaxnreg). The kernel launches with REGS_LAUNCH registers per thread; the
-// producer warpgroup gives registers back and the two epilogue warpgroups take them. The
+// producer warpgroup gives registers back and the epilogue warpgroups take them. The
 // hardware hands out only what this CTA released, and setmaxnreg.inc waits (without a bound)
 // until it is available, so the three counts MUST satisfy the inequality below.
-constexpr int REGS_LAUNCH = 168;    // 65536 / 384 rounded down to a multiple of 8
-constexpr int REGS_PRODUCER = 56;
-constexpr int REGS_EPILOGUE = 224;
+constexpr int REGS_LAUNCH = (65536 / BLOCK) / 8 * 8;            // 168 at 384 threads, 96 at 640
+constexpr int REGS_PRODUCER = (EPI_WGS == 2) ? 56 : 40;
+constexpr int REGS_EPILOGUE = ((BLOCK * REGS_LAUNCH - 128 * REGS_PRODUCER) / N_EPI) / 8 * 8;  // 224 / 104
 static_assert(128 * REGS_PRODUCER + N_EPI * REGS_EPILOGUE <= BLOCK * REGS_LAUNCH,
               "setmaxnreg.inc would wait forever: the epilogue asks for more registers than the producers release");
 static_assert(REGS_LAUNCH * BLOCK <= 65536, "launch register count exceeds the register file");
 
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t IDESC = umma_idesc_e4m3_f32(128, 256);
+constexpr uint32_t IDESC = umma_idesc_e4m3_f32(128, BC);
 
 // wait sites reported in the status word
 enum Site : uint32_t {
@@ -374,18 +409,14 @@ __device__ __forceinline__ void quantize_activations(const Params& p, int gwarp,
 // ------------------------------------------------------------------ shared state
 struct __align__(16) SharedState {
   uint64_t fullA[4], emptyA[4], fullB[4], emptyB[4];
-  uint64_t tmem_full[2], tmem_empty[2];
+  uint64_t tmem_full[NBUF], tmem_empty[NBUF];
   uint64_t inter_ready;
   uint32_t tmem_base;
   uint32_t flag;          // grid_sync result broadcast
   int n_my_tiles;
   int total_tiles;
   TileInfo tiles[MAX_MY_TILES];
-  int scan_cnt[E];
-  int scan_tile[E];
-  int tot[E];
-  int pre[E];
-  float rowmax[2][2][TILE_M];
+  float rowmax[2][EPI_WGS][TILE_M];
 };
 static_assert(sizeof(SharedState) <= SMEM_STATIC_RESERVE, "static shared state exceeds its reserve");
 
@@ -411,6 +442,10 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
   float* wsu_sm = as_sm + NK * TILE_M;                                    // [2][WSU_N]
   float* wsd_sm = wsu_sm + 2 * WSU_N;                                     // [2][WSD_N]
   int* hist = reinterpret_cast<int*>(a_ring);  // [NWARPS][E], phases 0-1 only
+  int* scan_cnt = reinterpret_cast<int*>(b_ring);  // phase 1 only: four arrays of E ints
+  int* scan_tile = scan_cnt + E;
+  int* ph1_tot = scan_tile + E;
+  int* ph1_pre = ph1_tot + E;
 
   if (bid == 0 && tid == 0) ws->phase_ns[0] = globaltimer_ns();
 
@@ -473,42 +508,42 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
 
   // ================================================================ phase 1
   if (alive) {
-    if (tid < E) { S.tot[tid] = 0; S.pre[tid] = 0; }
+    if (tid < E) { ph1_tot[tid] = 0; ph1_pre[tid] = 0; }
     __syncthreads();
     {
-      // 64 column groups of 4 experts x 6 row groups of CTAs
+      // 64 column groups of 4 experts x BLOCK/64 row groups of CTAs
       const int col = tid & 63, rg = tid >> 6;
       int4 tot = make_int4(0, 0, 0, 0), pre = make_int4(0, 0, 0, 0);
 #pragma unroll 5
-      for (int b = rg; b < kGrid; b += 6) {
+      for (int b = rg; b < kGrid; b += BLOCK / 64) {
         const int4 c = __ldcg(reinterpret_cast<const int4*>(&ws->cta_hist[b][col * 4]));
         tot.x += c.x; tot.y += c.y; tot.z += c.z; tot.w += c.w;
         if (b < bid) { pre.x += c.x; pre.y += c.y; pre.z += c.z; pre.w += c.w; }
       }
-      atomicAdd(&S.tot[col * 4 + 0], tot.x); atomicAdd(&S.tot[col * 4 + 1], tot.y);
-      atomicAdd(&S.tot[col * 4 + 2], tot.z); atomicAdd(&S.tot[col * 4 + 3], tot.w);
-      atomicAdd(&S.pre[col * 4 + 0], pre.x); atomicAdd(&S.pre[col * 4 + 1], pre.y);
-      atomicAdd(&S.pre[col * 4 + 2], pre.z); atomicAdd(&S.pre[col * 4 + 3], pre.w);
+      atomicAdd(&ph1_tot[col * 4 + 0], tot.x); atomicAdd(&ph1_tot[col * 4 + 1], tot.y);
+      atomicAdd(&ph1_tot[col * 4 + 2], tot.z); atomicAdd(&ph1_tot[col * 4 + 3], tot.w);
+      atomicAdd(&ph1_pre[col * 4 + 0], pre.x); atomicAdd(&ph1_pre[col * 4 + 1], pre.y);
+      atomicAdd(&ph1_pre[col * 4 + 2], pre.z); atomicAdd(&ph1_pre[col * 4 + 3], pre.w);
     }
     __syncthreads();
     int cnt = 0, tiles_e = 0;
     if (tid < E) {
-      cnt = S.tot[tid];
+      cnt = ph1_tot[tid];
       tiles_e = (cnt + TILE_M - 1) / TILE_M;
-      S.scan_cnt[tid] = cnt;
-      S.scan_tile[tid] = tiles_e;
+      scan_cnt[tid] = cnt;
+      scan_tile[tid] = tiles_e;
     }
     __syncthreads();
     for (int d = 1; d < E; d <<= 1) {
       int vc = 0, vt = 0;
-      if (tid < E && tid >= d) { vc = S.scan_cnt[tid - d]; vt = S.scan_tile[tid - d]; }
+      if (tid < E && tid >= d) { vc = scan_cnt[tid - d]; vt = scan_tile[tid - d]; }
       __syncthreads();
-      if (tid < E) { S.scan_cnt[tid] += vc; S.scan_tile[tid] += vt; }
+      if (tid < E) { scan_cnt[tid] += vc; scan_tile[tid] += vt; }
       __syncthreads();
     }
     if (tid < E) {
-      const int off_e = S.scan_cnt[tid] - cnt;
-      const int tbase = S.scan_tile[tid] - tiles_e;
+      const int off_e = scan_cnt[tid] - cnt;
+      const int tbase = scan_tile[tid] - tiles_e;
       if (tid == E - 1) S.total_tiles = tbase + tiles_e;
       if (bid == 0) {
         ws->expert_counts[tid] = cnt;
@@ -535,7 +570,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         }
       }
       // turn the per-warp histograms into per-warp write cursors
-      int base = off_e + S.pre[tid];
+      int base = off_e + ph1_pre[tid];
 #pragma unroll
       for (int w = 0; w < NWARPS; ++w) {
         const int h = hist[w * E + tid];
@@ -569,7 +604,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
   if (tid == 0) {
     for (int s = 0; s < SA; ++s) { mbar_init(&S.fullA[s], N_GATHER); mbar_init(&S.emptyA[s], 1); }
     for (int s = 0; s < SB; ++s) { mbar_init(&S.fullB[s], 1); mbar_init(&S.emptyB[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&S.tmem_full[s], 1); mbar_init(&S.tmem_empty[s], N_EPI / 32); }
+    for (int s = 0; s < NBUF; ++s) { mbar_init(&S.tmem_full[s], 1); mbar_init(&S.tmem_empty[s], N_EPI / 32); }
     mbar_init(&S.inter_ready, N_EPI / 32);
     mbar_init_fence();
   }
@@ -603,14 +638,21 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               { PROF_T0();
               if (!mbar_wait(&S.emptyB[st], ph ^ 1u, wc, kSiteEmptyB)) { ok = false; break; }
               PROF_ADD(pw_emptyB); }
-              mbar_arrive_expect_tx(&S.fullB[st], B_STAGE_BYTES);
+              mbar_arrive_expect_tx(&S.fullB[st], (MONO_ABLATE & 16) ? 0 : B_STAGE_BYTES);
+              if constexpr ((MONO_ABLATE & 16) != 0) { ++nb; continue; }
               uint8_t* dst = b_ring + st * B_STAGE_BYTES;
               const uint32_t x = static_cast<uint32_t>(ks * 128);
-              // shared rows [0,64) gate c..c+63 | [64,128) up c..c+63 | [128,192) gate c+64.. | [192,256) up c+64..
-              tma_load_2d(&p.tm_up, x, yg, dst, &S.fullB[st]);
-              tma_load_2d(&p.tm_up, x, yu, dst + 8192, &S.fullB[st]);
-              tma_load_2d(&p.tm_up, x, yg + 64, dst + 16384, &S.fullB[st]);
-              tma_load_2d(&p.tm_up, x, yu + 64, dst + 24576, &S.fullB[st]);
+              // shared rows of buffer j, warpgroup h: [j*BC + h*WC, +HCB) gate columns c + j*PASS_STRIDE + h*HCB ..,
+              // then the HCB matching up columns
+#pragma unroll
+              for (int j = 0; j < NSPLIT; ++j) {
+#pragma unroll
+                for (int hh = 0; hh < EPI_WGS; ++hh) {
+                  const uint32_t co = static_cast<uint32_t>(j * PASS_STRIDE + hh * HCB);
+                  tma_load_2d(&p.tm_up, x, yg + co, dst + (j * BC + hh * WC) * 128, &S.fullB[st]);
+                  tma_load_2d(&p.tm_up, x, yu + co, dst + (j * BC + hh * WC + HCB) * 128, &S.fullB[st]);
+                }
+              }
               ++nb;
             }
           }
@@ -619,13 +661,12 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             for (int dk = 0; dk < NP; ++dk) {
               const uint32_t st = nb % SB, ph = (nb / SB) & 1u;
               if (!mbar_wait(&S.emptyB[st], ph ^ 1u, wc, kSiteEmptyB)) { ok = false; break; }
-              mbar_arrive_expect_tx(&S.fullB[st], B_STAGE_BYTES);
+              mbar_arrive_expect_tx(&S.fullB[st], (MONO_ABLATE & 16) ? 0 : B_STAGE_BYTES);
+              if constexpr ((MONO_ABLATE & 16) != 0) { ++nb; continue; }
               uint8_t* dst = b_ring + st * B_STAGE_BYTES;
               const uint32_t x = static_cast<uint32_t>(dk * 128);
-              tma_load_2d(&p.tm_down, x, y, dst, &S.fullB[st]);
-              tma_load_2d(&p.tm_down, x, y + 64, dst + 8192, &S.fullB[st]);
-              tma_load_2d(&p.tm_down, x, y + 128, dst + 16384, &S.fullB[st]);
-              tma_load_2d(&p.tm_down, x, y + 192, dst + 24576, &S.fullB[st]);
+#pragma unroll
+              for (int j = 0; j < 256 / HCB; ++j) tma_load_2d(&p.tm_down, x, y + j * HCB, dst + j * HCB * 128, &S.fullB[st]);
               ++nb;
             }
           }
@@ -644,26 +685,32 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         const uint32_t a_ring_u32 = smem_u32(a_ring), b_ring_u32 = smem_u32(b_ring), inter_u32 = smem_u32(inter);
         for (int it = 0; it < n_my && ok; ++it) {
           for (int s = 0; s < NP * NK; ++s) {
-            const uint32_t sb = nb % SB, sa = na % SA, buf = nt & 1u;
+            const uint32_t sb = nb % SB, sa = na % SA;
             { PROF_T0();
             if (!mbar_wait(&S.fullB[sb], (nb / SB) & 1u, wc, kSiteFullB)) { ok = false; break; }
             PROF_ADD(pm_fullB); }
             { PROF_T0();
             if (!mbar_wait(&S.fullA[sa], (na / SA) & 1u, wc, kSiteFullA)) { ok = false; break; }
             PROF_ADD(pm_fullA); }
-            { PROF_T0();
-            if (!mbar_wait(&S.tmem_empty[buf], ((nt >> 1) & 1u) ^ 1u, wc, kSiteTmemEmpty)) { ok = false; break; }
-            PROF_ADD(pm_tmem); }
-            tc_fence_after();
             const uint64_t da = umma_desc_sw128(a_ring_u32 + sa * A_STAGE_BYTES);
-            const uint64_t db = umma_desc_sw128(b_ring_u32 + sb * B_STAGE_BYTES);
-            const uint32_t d = tmem_base + buf * 256u;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+            for (int j = 0; j < NSPLIT; ++j) {
+              const uint32_t buf = nt % NBUF;
+              { PROF_T0();
+              if (!mbar_wait(&S.tmem_empty[buf], ((nt / NBUF) & 1u) ^ 1u, wc, kSiteTmemEmpty)) { ok = false; break; }
+              PROF_ADD(pm_tmem); }
+              tc_fence_after();
+              const uint64_t db = umma_desc_sw128(b_ring_u32 + sb * B_STAGE_BYTES + j * BC * 128);
+              const uint32_t d = tmem_base + buf * BC;
+#pragma unroll
+              for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+              umma_commit(&S.tmem_full[buf]);
+              ++nt;
+            }
+            if (!ok) break;
             umma_commit(&S.emptyA[sa]);
             umma_commit(&S.emptyB[sb]);
-            umma_commit(&S.tmem_full[buf]);
-            ++nb; ++na; ++nt;
+            ++nb; ++na;
           }
           if (!ok) break;
           { PROF_T0();
@@ -672,22 +719,28 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
           tc_fence_after();
           for (int s = 0; s < NHB * NP; ++s) {
             const int dk = s % NP;
-            const uint32_t sb = nb % SB, buf = nt & 1u;
+            const uint32_t sb = nb % SB;
             { PROF_T0();
             if (!mbar_wait(&S.fullB[sb], (nb / SB) & 1u, wc, kSiteFullB)) { ok = false; break; }
             PROF_ADD(pm_fullB); }
-            { PROF_T0();
-            if (!mbar_wait(&S.tmem_empty[buf], ((nt >> 1) & 1u) ^ 1u, wc, kSiteTmemEmpty)) { ok = false; break; }
-            PROF_ADD(pm_tmem); }
-            tc_fence_after();
             const uint64_t da = umma_desc_sw128(inter_u32 + dk * A_STAGE_BYTES);
-            const uint64_t db = umma_desc_sw128(b_ring_u32 + sb * B_STAGE_BYTES);
-            const uint32_t d = tmem_base + buf * 256u;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+            for (int j = 0; j < NSPLIT; ++j) {
+              const uint32_t buf = nt % NBUF;
+              { PROF_T0();
+              if (!mbar_wait(&S.tmem_empty[buf], ((nt / NBUF) & 1u) ^ 1u, wc, kSiteTmemEmpty)) { ok = false; break; }
+              PROF_ADD(pm_tmem); }
+              tc_fence_after();
+              const uint64_t db = umma_desc_sw128(b_ring_u32 + sb * B_STAGE_BYTES + j * BC * 128);
+              const uint32_t d = tmem_base + buf * BC;
+#pragma unroll
+              for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+              umma_commit(&S.tmem_full[buf]);
+              ++nt;
+            }
+            if (!ok) break;
             umma_commit(&S.emptyB[sb]);
-            umma_commit(&S.tmem_full[buf]);
-            ++nb; ++nt;
+            ++nb;
           }
         }
 #ifdef MONO_PROFILE
@@ -697,16 +750,18 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         PROF_STORE(5, pm_total);
       }
     } else {
-      // ---------------------------------------------------------- activation gather (64 threads)
+      // ---------------------------------------------------------- activation gather (warps 2-3, 64 threads)
+      // cp.async 16 B with the 128-byte swizzle applied by hand; thread g copies rows g and g+64.
+      // (TMA tile::gather4 was measured here as well: correct, but a third slower than this path
+      // because every gathered row is a separate 128-byte request.)
       const int gt = tid - WARP_GATHER0 * 32;
       uint32_t na = 0;
       bool ok = true;
-      PROF_DECL(pg_emptyA); PROF_DECL(pg_cpwait);
+      PROF_DECL(pg_emptyA);
       const uint32_t a_ring_u32 = smem_u32(a_ring);
       for (int it = 0; it < n_my && ok; ++it) {
         const TileInfo ti = S.tiles[it];
         const uint8_t* src[2];
-        uint32_t off[2][8];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int r = gt + h * 64;
@@ -715,8 +770,6 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             const int fi = __ldcg(&p.sorted_ids[ti.row0 + r]);
             if (fi >= 0 && fi < numel) src[h] = p.act_fp8 + static_cast<size_t>(fi / TOP_K) * K_DIM;
           }
-#pragma unroll
-          for (int c = 0; c < 8; ++c) off[h][c] = sw128(r, c);
         }
         for (int s = 0; s < NP * NK; ++s) {
           const int ks = s % NK;
@@ -727,10 +780,10 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
           const uint32_t dst = a_ring_u32 + sa * A_STAGE_BYTES;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            if (src[h] != nullptr) {
+            if (src[h] != nullptr && (MONO_ABLATE & 8) == 0) {
               const uint8_t* g = src[h] + ks * 128;
 #pragma unroll
-              for (int c = 0; c < 8; ++c) cp_async16(dst + off[h][c], g + c * 16);
+              for (int c = 0; c < 8; ++c) cp_async16(dst + sw128(gt + h * 64, c), g + c * 16);
             }
           }
           // the barrier receives this thread's arrival when the copies above have landed
@@ -740,51 +793,65 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       }
       cp_async_commit();
       cp_async_wait<0>();
-      if (gt == 0) { PROF_STORE(6, pg_emptyA); PROF_STORE(7, pg_cpwait); }
+      if (gt == 0) { PROF_STORE(6, pg_emptyA); }
     }
     __syncwarp();
     reg_inc<REGS_LAUNCH>();
   } else {
-    // ------------------------------------------------------------ epilogue (256 threads)
+    // ------------------------------------------------------------ epilogue (EPI_WGS x 128 threads)
     reg_inc<REGS_EPILOGUE>();
     {
       const int et = tid - 128;
-      const int h = et >> 7;               // which 128 TMEM columns of the 256-column buffer
+      const int h = et >> 7;               // warpgroup: which WC columns of every accumulator buffer
       const int q = warp & 3;              // TMEM lane quarter this warp may read
       const int r = q * 32 + lane;         // row of the tile
-      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(h * 128);
+      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(h * WC);
       uint32_t nt = 0;
       bool dead = false;  // after an abort: keep the loop structure (named barriers stay matched), skip the work
-      float2 acc[64];     // pairs of adjacent columns; [0,32) gate (or down cols 0..63), [32,64) up (down cols 64..127)
+      // Accumulators, pairs of adjacent columns. Buffer j of a slab owns acc[j*WC/2, (j+1)*WC/2):
+      // first the HCB gate columns (down projection: the first half of WC output columns), then the up columns.
+      float2 acc[TCOLS / 2];
       PROF_DECL(pe_bar); PROF_DECL(pe_zero); PROF_DECL(pe_wait); PROF_DECL(pe_up); PROF_DECL(pe_silu); PROF_DECL(pe_down); PROF_DECL(pe_store);
 #ifdef MONO_PROFILE
       const long long pe_start = clock64();
 #endif
 
-      // one 128-deep K slab: acc += D * scale, 64 TMEM columns per load, packed fp32x2 FMAs
-      auto promote = [&](uint32_t buf, float s_lo, float s_hi) {
+      // Read one accumulator buffer out of tensor memory and fold it into part j of the register
+      // accumulators: acc += D * scale (s_lo for the first HCB columns, s_hi for the rest). The
+      // buffer goes back to the MMA thread as soon as its contents are in registers.
+      auto promote = [&](int j, uint32_t buf, float s_lo, float s_hi) {
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v[64];
-          tmem_ld64(t_lane + buf * 256u + c * 64u, v);
-          tmem_ld_wait();
-          const float sc = (c == 0) ? s_lo : s_hi;
-          const float2 s2 = make_float2(sc, sc);
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            acc[c * 32 + j] = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])), s2,
-                                         acc[c * 32 + j]);
+        if constexpr ((MONO_ABLATE & 1) != 0) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&S.tmem_empty[buf]);
+          return;
         }
-        // one arrival per warp: 256 per-thread arrivals on one shared-memory word serialise
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&S.tmem_empty[buf]);
+#pragma unroll
+        for (int c = 0; c < NLD; ++c) {
+          uint32_t v[LDW];
+          tmem_ld_n<LDW>(t_lane + buf * BC + c * LDW, v);
+          tmem_ld_wait();
+          if (c == NLD - 1) {
+            // one arrival per warp: per-thread arrivals on one shared-memory word serialise
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&S.tmem_empty[buf]);
+          }
+#pragma unroll
+          for (int i = 0; i < LDW / 2; ++i) {
+            const int pair = c * (LDW / 2) + i;              // pair of columns inside this warpgroup's WC
+            const float sc = (pair < HCB / 2) ? s_lo : s_hi;
+            acc[j * (WC / 2) + pair] = __ffma2_rn(make_float2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])),
+                                                  make_float2(sc, sc), acc[j * (WC / 2) + pair]);
+          }
+        }
       };
 
       // Scales are staged in shared memory one tile ahead: nothing in the slab loop waits on a
       // global load. stage_* below fetch tile `nx`: its row's slot id, routing weight and
-      // activation scales, and the expert's weight scales (into buffer nx & 1).
+      // activation scales (warpgroups 0 and 1 load half a row each), and the expert's weight
+      // scales (into buffer nx & 1).
       int nfi = -1;
       float nrw = 0.f, wsu_v = 0.f, wsd_v = 0.f;
       float4 as_v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -813,12 +880,14 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       };
       auto as_piece_load = [&](int j) {
         as_v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (nfi >= 0)
+        if (h < 2 && nfi >= 0)
           as_v = __ldcg(reinterpret_cast<const float4*>(p.act_scales + static_cast<size_t>(nfi / TOP_K) * NK + h * (NK / 2) + 4 * j));
       };
       auto as_piece_store = [&](int j) {
-        float* d = as_sm + (h * (NK / 2) + 4 * j) * TILE_M + r;
-        d[0] = as_v.x; d[TILE_M] = as_v.y; d[2 * TILE_M] = as_v.z; d[3 * TILE_M] = as_v.w;
+        if (h < 2) {
+          float* d = as_sm + (h * (NK / 2) + 4 * j) * TILE_M + r;
+          d[0] = as_v.x; d[TILE_M] = as_v.y; d[2 * TILE_M] = as_v.z; d[3 * TILE_M] = as_v.w;
+        }
       };
       if (n_my > 0) {
         stage_ids(0);
@@ -832,7 +901,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         const float rw = nrw;
         const float2 rw2 = make_float2(rw, rw);
         const float* wsu_t = wsu_sm + (it & 1) * WSU_N;
-        const float* wsd_t = wsd_sm + (it & 1) * WSD_N + h * NP;
+        const float* wsd_t = wsd_sm + (it & 1) * WSD_N;
         const bool has_next = it + 1 < n_my;
         float iscale[NP];
         { PROF_T0();
@@ -843,44 +912,56 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         for (int ps = 0; ps < NP; ++ps) {
           { PROF_T0();
 #pragma unroll
-          for (int i = 0; i < 64; ++i) acc[i] = make_float2(0.f, 0.f);
+          for (int i = 0; i < TCOLS / 2; ++i) acc[i] = make_float2(0.f, 0.f);
           PROF_ADD(pe_zero); }
           for (int ks = 0; ks < NK; ++ks) {
             const float a_s = as_sm[ks * TILE_M + r];
-            const float w_g = wsu_t[ps * NK + ks], w_u = wsu_t[(NP + ps) * NK + ks];
-            const uint32_t buf = nt & 1u;
-            { PROF_T0();
-            if (!dead && !mbar_wait(&S.tmem_full[buf], (nt >> 1) & 1u, wc, kSiteTmemFull)) dead = true;
-            PROF_ADD(pe_wait); }
-            PROF_T0();
-            if (!dead) promote(buf, __fmul_rn(w_g, a_s), __fmul_rn(w_u, a_s));
-            PROF_ADD(pe_up);
-            ++nt;
+            const float s_g = __fmul_rn(wsu_t[ps * NK + ks], a_s), s_u = __fmul_rn(wsu_t[(NP + ps) * NK + ks], a_s);
+#pragma unroll
+            for (int j = 0; j < NSPLIT; ++j) {
+              const uint32_t buf = nt % NBUF;
+              { PROF_T0();
+              if (!dead && !mbar_wait(&S.tmem_full[buf], (nt / NBUF) & 1u, wc, kSiteTmemFull)) dead = true;
+              PROF_ADD(pe_wait); }
+              PROF_T0();
+              if (!dead) promote(j, buf, s_g, s_u);
+              PROF_ADD(pe_up);
+              ++nt;
+            }
           }
           PROF_T0();
           if (p.dbg_acc != nullptr && fi >= 0 && !dead) {
             float* d = p.dbg_acc + static_cast<size_t>(ti.row0 + r) * N_UP;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              d[ps * 128 + h * 64 + 2 * j] = acc[j].x;
-              d[ps * 128 + h * 64 + 2 * j + 1] = acc[j].y;
-              d[N_HALF + ps * 128 + h * 64 + 2 * j] = acc[32 + j].x;
-              d[N_HALF + ps * 128 + h * 64 + 2 * j + 1] = acc[32 + j].y;
+            for (int j = 0; j < NSPLIT; ++j) {
+              const int col0 = ps * 128 + j * PASS_STRIDE + h * HCB;
+#pragma unroll
+              for (int i = 0; i < HCB / 2; ++i) {
+                d[col0 + 2 * i] = acc[j * (WC / 2) + i].x;
+                d[col0 + 2 * i + 1] = acc[j * (WC / 2) + i].y;
+                d[N_HALF + col0 + 2 * i] = acc[j * (WC / 2) + HCB / 2 + i].x;
+                d[N_HALF + col0 + 2 * i + 1] = acc[j * (WC / 2) + HCB / 2 + i].y;
+              }
             }
           }
-          // SiLU(gate) * up (kernel/qwen_tp/src/prefill_mono_final_nb.cu:678), written over the gate half
+          // SiLU(gate) * up (kernel/qwen_tp/src/prefill_mono_final_nb.cu:678), written over the gate columns
           float mx = 0.f;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float g0 = acc[j].x, g1 = acc[j].y;
-            const float v0 = __fdividef(acc[32 + j].x * g0, 1.0f + __expf(-g0));
-            const float v1 = __fdividef(acc[32 + j].y * g1, 1.0f + __expf(-g1));
-            acc[j] = make_float2(v0, v1);
-            mx = fmaxf(mx, fmaxf(fabsf(v0), fabsf(v1)));
+          for (int j = 0; j < ((MONO_ABLATE & 2) ? 0 : NSPLIT); ++j) {
+#pragma unroll
+            for (int i = 0; i < HCB / 2; ++i) {
+              const float2 g = acc[j * (WC / 2) + i], u = acc[j * (WC / 2) + HCB / 2 + i];
+              const float v0 = __fdividef(u.x * g.x, 1.0f + __expf(-g.x));
+              const float v1 = __fdividef(u.y * g.y, 1.0f + __expf(-g.y));
+              acc[j * (WC / 2) + i] = make_float2(v0, v1);
+              mx = fmaxf(mx, fmaxf(fabsf(v0), fabsf(v1)));
+            }
           }
+          // the row's amax over the pass's 128 columns: every warpgroup holds NSPLIT*HCB of them
           S.rowmax[ps & 1][h][r] = mx;
           named_bar_sync(1, N_EPI);
-          mx = fmaxf(mx, S.rowmax[ps & 1][h ^ 1][r]);
+#pragma unroll
+          for (int hh = 0; hh < EPI_WGS; ++hh) mx = fmaxf(mx, S.rowmax[ps & 1][hh][r]);
           const bool nz = mx > FLT_MIN;
           const float inv = nz ? __fdiv_rn(448.0f, mx) : 0.f;
           const float my_scale = nz ? __fdiv_rn(mx, 448.0f) : (1.0f / 448.0f);
@@ -889,15 +970,20 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             if (qq == ps) iscale[qq] = my_scale;  // static indexing keeps the array in registers
           uint8_t* irow = inter + ps * A_STAGE_BYTES;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint4 qv;
-            qv.x = pack_e4m3x4(acc[c * 8 + 0].x * inv, acc[c * 8 + 0].y * inv, acc[c * 8 + 1].x * inv, acc[c * 8 + 1].y * inv);
-            qv.y = pack_e4m3x4(acc[c * 8 + 2].x * inv, acc[c * 8 + 2].y * inv, acc[c * 8 + 3].x * inv, acc[c * 8 + 3].y * inv);
-            qv.z = pack_e4m3x4(acc[c * 8 + 4].x * inv, acc[c * 8 + 4].y * inv, acc[c * 8 + 5].x * inv, acc[c * 8 + 5].y * inv);
-            qv.w = pack_e4m3x4(acc[c * 8 + 6].x * inv, acc[c * 8 + 6].y * inv, acc[c * 8 + 7].x * inv, acc[c * 8 + 7].y * inv);
-            *reinterpret_cast<uint4*>(irow + sw128(r, h * 4 + c)) = qv;
-            if (p.dbg_inter != nullptr && fi >= 0 && !dead)
-              *reinterpret_cast<uint4*>(p.dbg_inter + static_cast<size_t>(ti.row0 + r) * N_HALF + ps * 128 + h * 64 + c * 16) = qv;
+          for (int j = 0; j < ((MONO_ABLATE & 2) ? 0 : NSPLIT); ++j) {
+#pragma unroll
+            for (int c = 0; c < HCB / 16; ++c) {
+              const float2* a = &acc[j * (WC / 2) + c * 8];
+              uint4 qv;
+              qv.x = pack_e4m3x4(a[0].x * inv, a[0].y * inv, a[1].x * inv, a[1].y * inv);
+              qv.y = pack_e4m3x4(a[2].x * inv, a[2].y * inv, a[3].x * inv, a[3].y * inv);
+              qv.z = pack_e4m3x4(a[4].x * inv, a[4].y * inv, a[5].x * inv, a[5].y * inv);
+              qv.w = pack_e4m3x4(a[6].x * inv, a[6].y * inv, a[7].x * inv, a[7].y * inv);
+              const int col0 = j * PASS_STRIDE + h * HCB + c * 16;  // column inside the pass's 128
+              *reinterpret_cast<uint4*>(irow + sw128(r, col0 / 16)) = qv;
+              if (p.dbg_inter != nullptr && fi >= 0 && !dead)
+                *reinterpret_cast<uint4*>(p.dbg_inter + static_cast<size_t>(ti.row0 + r) * N_HALF + ps * 128 + col0) = qv;
+            }
           }
           if (p.dbg_inter_scale != nullptr && fi >= 0 && h == 0 && !dead)
             p.dbg_inter_scale[static_cast<size_t>(ti.row0 + r) * NP + ps] = my_scale;
@@ -914,37 +1000,44 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         if (has_next) stage_ids(it + 1);
         for (int hb = 0; hb < NHB; ++hb) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) acc[i] = make_float2(0.f, 0.f);
+          for (int i = 0; i < TCOLS / 2; ++i) acc[i] = make_float2(0.f, 0.f);
           if (has_next) {
             if (hb == 1) stage_weight_store(it + 1);
             if (hb >= 1 && hb - 1 < AS_PIECES) as_piece_load(hb - 1);
           }
 #pragma unroll
           for (int dk = 0; dk < NP; ++dk) {
-            const float sc = __fmul_rn(wsd_t[hb * 2 * NP + dk], iscale[dk]);
-            const uint32_t buf = nt & 1u;
-            { PROF_T0();
-            if (!dead && !mbar_wait(&S.tmem_full[buf], (nt >> 1) & 1u, wc, kSiteTmemFull)) dead = true;
-            PROF_ADD(pe_wait); }
-            PROF_T0();
-            if (!dead) promote(buf, sc, sc);
-            PROF_ADD(pe_down);
-            ++nt;
+#pragma unroll
+            for (int j = 0; j < NSPLIT; ++j) {
+              // output columns hb*256 + j*BC + h*WC ..: one [128,128] weight-scale block
+              const float sc = __fmul_rn(wsd_t[(hb * 2 + (j * BC + h * WC) / 128) * NP + dk], iscale[dk]);
+              const uint32_t buf = nt % NBUF;
+              { PROF_T0();
+              if (!dead && !mbar_wait(&S.tmem_full[buf], (nt / NBUF) & 1u, wc, kSiteTmemFull)) dead = true;
+              PROF_ADD(pe_wait); }
+              PROF_T0();
+              if (!dead) promote(j, buf, sc, sc);
+              PROF_ADD(pe_down);
+              ++nt;
+            }
           }
           PROF_T0();
-          if (fi >= 0 && !dead) {
-            __nv_bfloat16* dst = p.partial + static_cast<size_t>(fi) * H_DIM + hb * 256 + h * 128;
+          if (fi >= 0 && !dead && (MONO_ABLATE & 4) == 0) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {  // 16 bf16 = 32 bytes per store: whole sectors
-              uint32_t w[8];
+            for (int j = 0; j < NSPLIT; ++j) {
+              __nv_bfloat16* dst = p.partial + static_cast<size_t>(fi) * H_DIM + hb * 256 + j * BC + h * WC;
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                // times the routing weight, then bf16 with saturation to the largest finite value
-                // (the clamp of kernel/qwen_tp/src/prefill_mono_final_nb.cu:916)
-                const float2 v = __fmul2_rn(acc[c * 8 + j], rw2);
-                w[j] = cvt_bf16x2_satfinite(v.x, v.y);
+              for (int c = 0; c < WC / 16; ++c) {  // 16 bf16 = 32 bytes per store: whole sectors
+                uint32_t w[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  // times the routing weight, then bf16 with saturation to the largest finite value
+                  // (the clamp of kernel/qwen_tp/src/prefill_mono_final_nb.cu:916)
+                  const float2 v = __fmul2_rn(acc[j * (WC / 2) + c * 8 + i], rw2);
+                  w[i] = cvt_bf16x2_satfinite(v.x, v.y);
+                }
+                st_global_256(dst + c * 16, w);
               }
-              st_global_256(dst + c * 16, w);
             }
           }
           if (has_next && hb >= 1 && hb - 1 < AS_PIECES) as_piece_store(hb - 1);
@@ -961,7 +1054,6 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
     }
     reg_dec<REGS_LAUNCH>();
   }
-
 
   // teardown of phase 2: when aborting, give in-flight bulk copies and MMAs time to land
   if (aborted(ws)) __nanosleep(200000);
@@ -1142,13 +1234,13 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D u8 tensor [rows, cols] row-major, box 64 rows x 128 bytes, 128-byte swizzle.
-int make_weight_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols) {
+// 2-D u8 tensor [rows, cols] row-major, box box_rows x 128 bytes, 128-byte swizzle.
+int make_u8_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return -1;
   cuuint64_t gd[2] = {cols, rows};
   cuuint64_t gs[1] = {cols};
-  cuuint32_t bx[2] = {128u, 64u};
+  cuuint32_t bx[2] = {128u, box_rows};
   cuuint32_t es[2] = {1u, 1u};
   const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gd, gs, bx, es,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1283,16 +1375,17 @@ int launch_prefill_moe_wgmma_q1_ep2(const float* logits, int num_tokens, int blo
   p.dbg_inter = g_dbg_inter;
   p.dbg_inter_scale = g_dbg_inter_scale;
 
-  int rc = make_weight_map(&p.tm_up, up_w_fp8, static_cast<uint64_t>(E_LOCAL) * N_UP, K_DIM);
+  int rc = make_u8_map(&p.tm_up, up_w_fp8, static_cast<uint64_t>(E_LOCAL) * N_UP, K_DIM, HCB);
   if (rc != 0) {
     fprintf(stderr, "up-projection tensor map failed: %d\n", rc);
     return -2;
   }
-  rc = make_weight_map(&p.tm_down, down_w_fp8, static_cast<uint64_t>(E_LOCAL) * H_DIM, N_HALF);
+  rc = make_u8_map(&p.tm_down, down_w_fp8, static_cast<uint64_t>(E_LOCAL) * H_DIM, N_HALF, HCB);
   if (rc != 0) {
     fprintf(stderr, "down-projection tensor map failed: %d\n", rc);
     return -3;
   }
+
 
   err = cudaFuncSetAttribute(moe_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM);
   if (err != cudaSuccess) return static_cast<int>(err);

@@ -147,6 +147,12 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&v)[64]) {
       : "r"(taddr)
       : "memory");
 }
+template <int N>
+__device__ __forceinline__ void tmem_ld_n(uint32_t taddr, uint32_t (&v)[N]) {
+  static_assert(N == 32 || N == 64, "32 or 64 columns per load");
+  if constexpr (N == 32) tmem_ld32(taddr, v);
+  else tmem_ld64(taddr, v);
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------- UMMA
