@@ -25,7 +25,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-from unimonomoe_b200 import MonoKernel, synth, variant_path  # noqa: E402
+from unimonomoe_b200 import MonoKernel, synth, tp_fused, variant_path  # noqa: E402
 
 NOMINAL_FP8_TFLOPS = 4500.0
 METRIC = "moe_layer_prefill_fp8_tflops"
@@ -195,6 +195,7 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--unfused", action="store_true", help="N>1: reduce with NCCL after the kernel instead of in-kernel")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end leg, the library GEMM probe and the CPU baseline (profiling runs)")
     args = ap.parse_args()
@@ -235,11 +236,36 @@ def main() -> None:
     out = torch.empty(T, spec.hidden, dtype=torch.bfloat16, device=dev)
     sc = mk.scratch(T, dev)
 
-    def step():
-        mk.prefill_impl(batch["hs"], batch["logits"], layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"],
-                        spec.top_k, True, None, out, expert_map=emap, scratch=sc)
-        if world > 1:
+    # N = 2, 4 (tensor parallel): the reduce runs inside the kernel (NVLS multimem through a symmetric
+    # pool) when every rank can; otherwise, and for expert parallelism, NCCL reduces after the kernel.
+    plan = None
+    if par.startswith("tp") and not args.unfused:
+        plan = tp_fused.FusedTPPlan(mk, dist.group.WORLD, hidden=spec.hidden, max_tokens=T)
+        if plan.usable and plan.chunks_for(T) == 0:
+            plan.chunks_by_tokens[T] = 8 if T >= 16384 else 4
+        if not plan.usable:
+            if rank == 0:
+                print(f"# fused TP epilogue unavailable ({plan.reason}); reducing with NCCL", file=sys.stderr)
+            plan = None
+    reduce_desc = "none" if world == 1 else (
+        f"in-kernel NVLS multimem all-reduce, {plan.chunks_for(T)} chunks, {plan.ncomm} communication CTAs"
+        if plan is not None else "NCCL all-reduce after the kernel")
+
+    def launch(hs, lg):
+        if plan is not None:
+            plan.fused_tp_launch(hs, lg, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k,
+                                 True, None)
+        else:
+            mk.prefill_impl(hs, lg, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k, True,
+                            None, out, expert_map=emap, scratch=sc)
+
+    def reduce_out():
+        if world > 1 and plan is None:
             dist.all_reduce(out)
+
+    def step():
+        launch(batch["hs"], batch["logits"])
+        reduce_out()
 
     def barrier():
         if world > 1:
@@ -259,11 +285,9 @@ def main() -> None:
         e0.record()
         for a, b in evs:
             a.record()
-            mk.prefill_impl(batch["hs"], batch["logits"], layer["w13"], layer["w13_scale"], layer["w2"],
-                            layer["w2_scale"], spec.top_k, True, None, out, expert_map=emap, scratch=sc)
+            launch(batch["hs"], batch["logits"])
             b.record()
-            if world > 1:
-                dist.all_reduce(out)
+            reduce_out()
         e1.record()
         barrier()
     total_ms = e0.elapsed_time(e1)
@@ -279,18 +303,20 @@ def main() -> None:
 
     e2e_ms = None
     if not args.kernel_only:
-        e2e_ms = time_e2e(args, mk, spec, layer, batch, out, emap, sc, world, dist, barrier, dev)
+        result = plan.pool.output(T) if plan is not None else out
+        e2e_ms = time_e2e(args, spec, batch, result, launch, reduce_out, world, dist, barrier, dev)
     h2d = batch["hs"].numel() * 2 + batch["logits"].numel() * 4
     d2h = out.numel() * 2
 
     if rank == 0:
-        report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev)
+        report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
+               reduce_desc)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
-def time_e2e(args, mk, spec, layer, batch, out, emap, sc, world, dist, barrier, dev) -> float:
+def time_e2e(args, spec, batch, out, launch, reduce_out, world, dist, barrier, dev) -> float:
     """End to end through the public API: host buffers in, host result out, copies inside the timed region."""
     T = batch["hs"].shape[0]
     hs_host = batch["hs"].cpu().pin_memory()
@@ -301,10 +327,8 @@ def time_e2e(args, mk, spec, layer, batch, out, emap, sc, world, dist, barrier, 
     def e2e_step():
         hs_dev.copy_(hs_host, non_blocking=True)
         lg_dev.copy_(lg_host, non_blocking=True)
-        mk.prefill_impl(hs_dev, lg_dev, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k,
-                        True, None, out, expert_map=emap, scratch=sc)
-        if world > 1:
-            dist.all_reduce(out)
+        launch(hs_dev, lg_dev)
+        reduce_out()
         out_host.copy_(out, non_blocking=True)
 
     for _ in range(3):
@@ -323,43 +347,43 @@ def time_e2e(args, mk, spec, layer, batch, out, emap, sc, world, dist, barrier, 
     return float(t[0])
 
 
-def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev) -> None:
-    if True:
-        peaks = measured_peaks()
-        fp8_lib = fp8_gemm_tflops(dev) if (world == 1 and not args.kernel_only) else None
-        if peaks.get("bf16_tflops"):
-            peak, peak_src = 2.0 * float(peaks["bf16_tflops"]), "2 x bf16_tflops (burst) of MEASURED_PEAKS.json: no fp8 figure is measured there"
-        else:
-            peak, peak_src = 2.0 * 1590.0, "2 x 1590 TFLOP/s bf16 fallback"
-        achieved = (flops / world) / (kern_ms * 1e-3) / 1e12
-        traffic = None
-        tp = os.path.join(ROOT, "profiles", "traffic.json")
-        if os.path.exists(tp):
-            try:
-                traffic = json.load(open(tp)).get(f"{variant}_T{T}")
-            except Exception:
-                traffic = None
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": f"{spec.name} MoE layer prefill, T={T} tokens, H=2048, E=256, top-8, I=512, "
-                                   f"block-FP8 [128,128] weights", "tokens": T, "parallelism": par, "variant": variant,
-                       "l2_policy": "inputs larger than L2: 805 MB of weights + 0.5 GB of partial rows stream per step",
-                       "reduce": "none" if world == 1 else "NCCL all-reduce after the kernel"},
-            "clocks": clk.summary(),
-            "e2e": (None if e2e_ms is None else
-                    {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
-                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}),
-            "gpu_launches": args.steps,
-            "kernel_ms": kern_ms,
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
-                         "traffic": traffic, "peak_source": peak_src, "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
-                         "library_fp8_gemm_tflops": fp8_lib},
-        }
-        if world == 1 and not args.no_cpu_baseline and not args.kernel_only:
-            line["cpu_baseline"] = time_cpu_baseline(spec, 256)
-        print(json.dumps(line), flush=True)
+def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
+           reduce_desc) -> None:
+    peaks = measured_peaks()
+    fp8_lib = fp8_gemm_tflops(dev) if (world == 1 and not args.kernel_only) else None
+    if peaks.get("bf16_tflops"):
+        peak, peak_src = 2.0 * float(peaks["bf16_tflops"]), "2 x bf16_tflops (burst) of MEASURED_PEAKS.json: no fp8 figure is measured there"
+    else:
+        peak, peak_src = 2.0 * 1590.0, "2 x 1590 TFLOP/s bf16 fallback"
+    achieved = (flops / world) / (kern_ms * 1e-3) / 1e12
+    traffic = None
+    tp = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tp):
+        try:
+            traffic = json.load(open(tp)).get(f"{variant}_T{T}")
+        except Exception:
+            traffic = None
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"{spec.name} MoE layer prefill, T={T} tokens, H=2048, E=256, top-8, I=512, "
+                               f"block-FP8 [128,128] weights", "tokens": T, "parallelism": par, "variant": variant,
+                   "l2_policy": "inputs larger than L2: 805 MB of weights + 0.5 GB of partial rows stream per step",
+                   "reduce": reduce_desc},
+        "clocks": clk.summary(),
+        "e2e": (None if e2e_ms is None else
+                {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}),
+        "gpu_launches": args.steps,
+        "kernel_ms": kern_ms,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+                     "traffic": traffic, "peak_source": peak_src, "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
+                     "library_fp8_gemm_tflops": fp8_lib},
+    }
+    if world == 1 and not args.no_cpu_baseline and not args.kernel_only:
+        line["cpu_baseline"] = time_cpu_baseline(spec, 256)
+    print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":

@@ -162,6 +162,7 @@ int prefill_wgmma_counts_offset(void);        /* i32 [E]   rows per local expert
 int prefill_wgmma_offsets_offset(void);       /* i32 [E+1] exclusive prefix sum */
 int prefill_wgmma_total_tiles_offset(void);   /* i32 */
 int prefill_wgmma_phase_ns_offset(void);      /* u64 [8] %globaltimer at phase boundaries */
+int prefill_wgmma_prof_offset(void);          /* u64 [148][16] stall counters, filled only by profiling builds */
 /* Debug dump targets for later launches (device pointers or null): raw gate|up sums
  * fp32 [T*k, 2*N_HALF], e4m3 intermediate [T*k, N_HALF], its scales fp32 [T*k, N_HALF/128],
  * indexed by sorted row. */

@@ -462,6 +462,9 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
   for (int i = tid; i < NWARPS * E; i += BLOCK) hist[i] = 0;
   __syncthreads();
 
+  // Every warp first routes its contiguous range of tokens, then quantises activations. (Splitting the
+  // warps into routers and quantisers was measured and is slower: routing is instruction-bound and
+  // wants all twelve warps.)
   const int gwarp = bid * NWARPS + warp;
   const int nwarps_grid = kGrid * NWARPS;
   const int tok_per_warp = (T + nwarps_grid - 1) / nwarps_grid;
@@ -1467,5 +1470,6 @@ int launch_prefill_moe_wgmma_q1_ep(const float* logits, int num_tokens, int bloc
                                          topk_ids, topk_weights, sorted_token_ids, bf16_output, router_bias, nullptr,
                                          nullptr, 0, 1, 1, 0, 0u, nullptr, nullptr, 1.0f, expert_map, stream);
 }
+
 
 }  // extern "C"
