@@ -168,6 +168,23 @@ int prefill_wgmma_prof_offset(void);          /* u64 [148][16] stall counters, f
  * indexed by sorted row. */
 void prefill_wgmma_set_debug(void* acc, void* inter, void* inter_scale);
 
+/* Launch that allocates nothing and needs no scratch from the caller. No counterpart in the
+ * reference. For hosts that cannot obtain device memory at call time (all of HBM already given to
+ * a KV-cache pool; callers that cannot take the device-wide synchronisation of cudaMalloc): the
+ * workspace, the e4m3 activations, routing results, sort permutation and partial rows live in a
+ * fixed array inside the library, prefill_wgmma_noalloc_scratch_bytes() per GPU for the life of
+ * the process. At most prefill_wgmma_noalloc_max_tokens() tokens (256 for H = 2048, 64 for
+ * H = 7168); more returns -130 and launches nothing; -131 if the array's address cannot be
+ * resolved. All calls on a device share the array: calls whose kernels overlap on the GPU race,
+ * so keep them ordered. The first call on each device looks the array up (cudaGetSymbolAddress);
+ * make it outside stream capture. expert_map and router_bias as in the _ep entry (null when unused). */
+int launch_prefill_moe_noalloc(const float* logits, int num_tokens, const void* act_bf16, const uint8_t* up_w_fp8,
+                               const float* up_w_scales, const uint8_t* down_w_fp8, const float* down_w_scales,
+                               void* bf16_output, const float* router_bias, const int32_t* expert_map,
+                               prefill_mono_stream_t stream);
+int prefill_wgmma_noalloc_max_tokens(void);
+size_t prefill_wgmma_noalloc_scratch_bytes(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1472,4 +1472,74 @@ int launch_prefill_moe_wgmma_q1_ep(const float* logits, int num_tokens, int bloc
 }
 
 
+// ---------------------------------------------------------------------------------------------
+// Launch without any allocation by the caller or by this library.
+//
+// Some hosts of this kernel cannot obtain device memory at call time: a serving engine that has
+// already handed every free byte of HBM to its KV-cache pool (a late cudaMalloc there fails, or
+// evicts what the engine reserved), and latency-sensitive callers for which the implicit
+// device-wide synchronisation of cudaMalloc / cudaFree stalls every other stream. For them the
+// scratch the kernel needs (workspace, e4m3 activations and their scales, routing results, the
+// sort permutation and the bf16 partial rows) lives in the fixed array below, which every GPU
+// that loads this library holds from load until the process exits. The caller passes only the
+// inputs and the output. The price is a cap on the batch: kNoAllocMaxTokens tokens.
+//
+// * All calls on one device share the array. It keeps the previous call's contents; the launch
+//   clears the part that must start at zero (the workspace). Two calls whose kernels overlap on
+//   the GPU (different streams, no ordering between them) race on it: serialise them.
+// * The first call on each device resolves the array's device address with cudaGetSymbolAddress
+//   (with that device current) and caches it; make that first call outside any stream capture.
+constexpr int kNoAllocMaxTokens = (H_DIM <= 2048) ? 256 : 64;
+constexpr size_t na_align(size_t x) { return (x + 255) / 256 * 256; }
+constexpr size_t kNaWorkspace = 0;
+constexpr size_t kNaActFp8 = kNaWorkspace + na_align(sizeof(Workspace));
+constexpr size_t kNaActScales = kNaActFp8 + na_align(static_cast<size_t>(kNoAllocMaxTokens) * K_DIM);
+constexpr size_t kNaTopkIds = kNaActScales + na_align(static_cast<size_t>(kNoAllocMaxTokens) * NK * 4);
+constexpr size_t kNaTopkW = kNaTopkIds + na_align(static_cast<size_t>(kNoAllocMaxTokens) * TOP_K * 4);
+constexpr size_t kNaSorted = kNaTopkW + na_align(static_cast<size_t>(kNoAllocMaxTokens) * TOP_K * 4);
+constexpr size_t kNaPartial = kNaSorted + na_align(static_cast<size_t>(kNoAllocMaxTokens) * TOP_K * 4);
+constexpr size_t kNaBytes = kNaPartial + na_align(static_cast<size_t>(kNoAllocMaxTokens) * TOP_K * H_DIM * 2);
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNaBytes];
+
+int prefill_wgmma_noalloc_max_tokens() { return kNoAllocMaxTokens; }
+size_t prefill_wgmma_noalloc_scratch_bytes() { return kNaBytes; }
+
+// Returns 0 on success; -130 when num_tokens exceeds prefill_wgmma_noalloc_max_tokens(); -131 when the
+// device address of the scratch array cannot be resolved; otherwise the codes of the other entry points.
+int launch_prefill_moe_noalloc(const float* logits, int num_tokens, const void* act_bf16, const uint8_t* up_w_fp8,
+                               const float* up_w_scales, const uint8_t* down_w_fp8, const float* down_w_scales,
+                               void* bf16_output, const float* router_bias, const int32_t* expert_map,
+                               cudaStream_t stream) {
+  if (num_tokens > kNoAllocMaxTokens) {
+    fprintf(stderr, "launch_prefill_moe_noalloc: %d tokens exceed the built-in scratch (max %d tokens)\n", num_tokens,
+            kNoAllocMaxTokens);
+    return -130;
+  }
+  // In host code the array's name is only a handle: the device address has to be asked for, once per
+  // device, with that device current.
+  constexpr int kMaxDevices = 64;
+  static unsigned char* base_of_device[kMaxDevices] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  if (dev < 0 || dev >= kMaxDevices) return -131;
+  if (base_of_device[dev] == nullptr) {
+    void* ptr = nullptr;
+    err = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (err != cudaSuccess || ptr == nullptr) {
+      fprintf(stderr, "launch_prefill_moe_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(err));
+      return -131;
+    }
+    base_of_device[dev] = static_cast<unsigned char*>(ptr);
+  }
+  unsigned char* b = base_of_device[dev];
+  return launch_prefill_moe_wgmma_q1_ep2(
+      logits, num_tokens, TILE_M, b + kNaWorkspace, sizeof(Workspace), act_bf16, b + kNaActFp8,
+      reinterpret_cast<float*>(b + kNaActScales), up_w_fp8, up_w_scales, down_w_fp8, down_w_scales,
+      reinterpret_cast<float*>(b + kNaPartial), reinterpret_cast<int32_t*>(b + kNaTopkIds),
+      reinterpret_cast<float*>(b + kNaTopkW), reinterpret_cast<int32_t*>(b + kNaSorted), bf16_output, router_bias,
+      nullptr, nullptr, 0, 1, 1, 0, 0u, nullptr, nullptr, 1.0f, expert_map, stream);
+}
+
 }  // extern "C"
