@@ -195,6 +195,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallel", default="auto", choices=["auto", "tp", "ep"],
+                    help="N>1: tensor parallel (N=2,4) or expert parallel; auto = ep")
     ap.add_argument("--unfused", action="store_true", help="N>1: reduce with NCCL after the kernel instead of in-kernel")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end leg, the library GEMM probe and the CPU baseline (profiling runs)")
@@ -220,7 +222,7 @@ def main() -> None:
     T = args.tokens
     if world == 1:
         variant, par, kw = "qwen_w1", "none", {}
-    elif world in (2, 4):
+    elif world in (2, 4) and args.parallel == "tp":
         variant, par = f"qwen_tp{world}", f"tp{world}"
         n = spec.inter // world
         kw = {"inter_slice": (rank * n, (rank + 1) * n)}
@@ -236,10 +238,12 @@ def main() -> None:
     out = torch.empty(T, spec.hidden, dtype=torch.bfloat16, device=dev)
     sc = mk.scratch(T, dev)
 
-    # N = 2, 4 (tensor parallel): the reduce runs inside the kernel (NVLS multimem through a symmetric
-    # pool) when every rank can; otherwise, and for expert parallelism, NCCL reduces after the kernel.
+    # N > 1: the all-reduce of the ranks' partial outputs runs inside the kernel (NVLS multimem through a
+    # symmetric pool) when every rank can; otherwise NCCL reduces after the kernel.
     plan = None
-    if par.startswith("tp") and not args.unfused:
+    # 32 communication CTAs measured best on B200 (14, 32 and 48 tried at four ranks)
+    os.environ.setdefault("VLLM_PREFILL_MONOKERNEL_TP_NCOMM", "32")
+    if world > 1 and not args.unfused:
         plan = tp_fused.FusedTPPlan(mk, dist.group.WORLD, hidden=spec.hidden, max_tokens=T)
         if plan.usable and plan.chunks_for(T) == 0:
             plan.chunks_by_tokens[T] = 8 if T >= 16384 else 4
@@ -254,7 +258,7 @@ def main() -> None:
     def launch(hs, lg):
         if plan is not None:
             plan.fused_tp_launch(hs, lg, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k,
-                                 True, None)
+                                 True, None, expert_map=emap)
         else:
             mk.prefill_impl(hs, lg, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k, True,
                             None, out, expert_map=emap, scratch=sc)

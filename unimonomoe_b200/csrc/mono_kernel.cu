@@ -1178,7 +1178,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         size_t s_lo = lo + (ng * sh / nsh) * ALIGN, s_hi = lo + (ng * (sh + 1) / nsh) * ALIGN;
         s_lo = s_lo < hi ? s_lo : hi;
         s_hi = s_hi < hi ? s_hi : hi;
-        constexpr int UN = 4;
+        constexpr int UN = 8;  // 16-byte reduce-loads in flight per thread: NVLink latency is covered by depth
         for (size_t base = s_lo + tid; base < s_hi; base += static_cast<size_t>(UN) * BLOCK) {
           uint32_t x[UN][4];
           bool live[UN];

@@ -252,9 +252,11 @@ class MonoKernel:
 
         emap = None
         if expert_map is not None:
-            if tp is not None:
-                raise RuntimeError("the fused TP collective and an expert_map cannot be combined; an EP rank's "
-                                   "output is reduced by the caller")
+            # The reference refuses the fused collective together with an expert_map (an EP rank's output is
+            # reduced by the caller, _custom_ops.py:4626-4633). Here the in-kernel reduce also serves expert
+            # parallelism: the partial sums of EP ranks are reduced exactly like those of TP ranks.
+            if tp is not None and not hasattr(self.lib, "launch_prefill_moe_wgmma_q1_ep2"):
+                raise RuntimeError("the fused collective and an expert_map need launch_prefill_moe_wgmma_q1_ep2")
             emap = expert_map.to(torch.int32).contiguous()
         bias = self.validate(activations_in, expert_weights_up, expert_weights_down, top_k,
                              e_score_correction_bias, emap)
@@ -295,11 +297,17 @@ class MonoKernel:
         bias_arg = vp(bias.data_ptr() if bias is not None else 0)
         if tp is not None:
             mc, pads, seqctr, rank, world, nchunk, ncomm = tp
-            entry = self.lib.launch_prefill_moe_wgmma_q1_tp2 if fold else self.lib.launch_prefill_moe_wgmma_q1_tp
             args += [bias_arg, vp(int(mc)), vp(int(pads)), ctypes.c_int(int(rank)), ctypes.c_int(int(world)),
                      ctypes.c_int(int(nchunk)), ctypes.c_int(int(ncomm)), ctypes.c_uint(0), vp(int(seqctr))]
-            if fold:
+            if emap is not None:
+                entry = self.lib.launch_prefill_moe_wgmma_q1_ep2
+                entry.restype = ctypes.c_int
+                args += [vp(int(resid_ptr)), ctypes.c_float(float(out_scale)), vp(emap.data_ptr())]
+            elif fold:
+                entry = self.lib.launch_prefill_moe_wgmma_q1_tp2
                 args += [vp(int(resid_ptr)), ctypes.c_float(float(out_scale))]
+            else:
+                entry = self.lib.launch_prefill_moe_wgmma_q1_tp
         elif emap is not None:
             if not self.has_ep:
                 raise RuntimeError("loaded monokernel .so has no launch_prefill_moe_wgmma_q1_ep")
@@ -334,7 +342,7 @@ class MonoKernel:
     def prefill_out(self, activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
                     expert_scales_down, out, top_k=8, renormalize=True, e_score_correction_bias=None, tp_mc_ptr=0,
                     tp_pads_ptr=0, tp_seqctr_ptr=0, tp_rank=0, tp_world=1, tp_nchunk=0, tp_ncomm=0, tp_residual=None,
-                    tp_out_scale=1.0, check=False) -> None:
+                    tp_out_scale=1.0, check=False, expert_map=None) -> None:
         """Write into a caller-supplied destination (_custom_ops.py:4861-4924). tp_ncomm > 0 selects the
         fused collective, in which case ``out`` must be the symmetric window tp_mc_ptr aliases."""
         tp = None
@@ -344,7 +352,7 @@ class MonoKernel:
             tp = (tp_mc_ptr, tp_pads_ptr, tp_seqctr_ptr, tp_rank, tp_world, tp_nchunk, tp_ncomm)
         self.prefill_impl(activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
                           expert_scales_down, top_k, renormalize, e_score_correction_bias, out, tp, tp_residual,
-                          tp_out_scale, check=check)
+                          tp_out_scale, expert_map, check=check)
 
 
 # ---------------------------------------------------------------------- module-level mirror

@@ -222,7 +222,8 @@ class FusedTPPlan:
         return any(p == self.pool.base_ptr(s) for s in range(self.pool.nslots))
 
     def fused_tp_launch(self, x, router_logits, w13, w13_scale, w2, w2_scale, top_k=8, renormalize=True,
-                        e_score_correction_bias=None, residual=None, out_scale=1.0, slot=0, check=False):
+                        e_score_correction_bias=None, residual=None, out_scale=1.0, slot=0, check=False,
+                        expert_map=None):
         """Launch with the in-kernel reduce when this token count is in the table; returns the pool
         view holding the REDUCED output, or None when the ordinary path must be taken
         (monokernel_tp.py:421-514). Deliberately no try/except: after the vote there is no fallback."""
@@ -240,5 +241,5 @@ class FusedTPPlan:
                                 e_score_correction_bias, tp_mc_ptr=self.pool.mc_ptr(slot),
                                 tp_pads_ptr=self.pool.pads_ptr, tp_seqctr_ptr=self.pool.seqctr_ptr,
                                 tp_rank=self.rank, tp_world=self.world, tp_nchunk=nchunk, tp_ncomm=self.ncomm,
-                                tp_residual=residual, tp_out_scale=out_scale, check=check)
+                                tp_residual=residual, tp_out_scale=out_scale, check=check, expert_map=expert_map)
         return out
