@@ -195,6 +195,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--model", default="qwen", choices=["qwen", "deepseek"],
+                    help="deepseek: DeepSeek-V3-like layer (H=7168, I=2048, grouped sigmoid router), tensor parallel, N=4 or 8")
     ap.add_argument("--parallel", default="auto", choices=["auto", "tp", "ep"],
                     help="N>1: tensor parallel (N=2,4) or expert parallel; auto = ep")
     ap.add_argument("--unfused", action="store_true", help="N>1: reduce with NCCL after the kernel instead of in-kernel")
@@ -218,9 +220,15 @@ def main() -> None:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
-    spec = synth.QWEN
+    spec = synth.QWEN if args.model == "qwen" else synth.DEEPSEEK
     T = args.tokens
-    if world == 1:
+    if args.model == "deepseek":
+        if world not in (4, 8):
+            raise SystemExit("the DeepSeek-V3 geometry is built as 1/4 and 1/8 width shards only: use --gpus 4 or 8")
+        variant, par = f"ds_tp{world}", f"tp{world}"
+        n = spec.inter // world
+        kw = {"inter_slice": (rank * n, (rank + 1) * n), "chunk": 8}
+    elif world == 1:
         variant, par, kw = "qwen_w1", "none", {}
     elif world in (2, 4) and args.parallel == "tp":
         variant, par = f"qwen_tp{world}", f"tp{world}"
@@ -258,10 +266,10 @@ def main() -> None:
     def launch(hs, lg):
         if plan is not None:
             plan.fused_tp_launch(hs, lg, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k,
-                                 True, None, expert_map=emap)
+                                 True, layer["bias"], expert_map=emap)
         else:
             mk.prefill_impl(hs, lg, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k, True,
-                            None, out, expert_map=emap, scratch=sc)
+                            layer["bias"], out, expert_map=emap, scratch=sc)
 
     def reduce_out():
         if world > 1 and plan is None:
