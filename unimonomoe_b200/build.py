@@ -37,8 +37,8 @@ VARIANTS = {
 # development variants (not built by default): other epilogue shapes, and the stall-counter build
 DEV_VARIANTS = {
     "qwen_w1_n2": dict(QWEN, N_HALF=512, E_LOCAL=256, EPI_WGS=2, NSPLIT=2),
-    "qwen_w1_e4": dict(QWEN, N_HALF=512, E_LOCAL=256, EPI_WGS=4, NSPLIT=1),
     "qwen_w1_prof": dict(QWEN, N_HALF=512, E_LOCAL=256, PROFILE=1),
+    "qwen_w1_plainst": dict(QWEN, N_HALF=512, E_LOCAL=256, PLAIN_STORES=1),
     **{f"qwen_w1_abl{m}": dict(QWEN, N_HALF=512, E_LOCAL=256, NSPLIT=1, ABLATE=m) for m in (1, 4, 7, 15, 23, 31)},
 }
 
@@ -68,7 +68,7 @@ def build_variant(variant: str, force: bool = False, verbose: bool = False) -> s
         "-Xptxas", "-v", "-shared", "-Xcompiler", "-fPIC",
         f"-DMONO_K_DIM={g['K']}", f"-DMONO_H_DIM={g['H']}", f"-DMONO_N_HALF={g['N_HALF']}",
         f"-DMONO_E_LOCAL={g['E_LOCAL']}", f"-DMONO_ROUTER_MODE={g['MODE']}", f"-DMONO_EPI_WGS={g.get('EPI_WGS', 2)}", f"-DMONO_NSPLIT={g.get('NSPLIT', 1)}",
-        *(["-DMONO_PROFILE"] if g.get("PROFILE") else []), f"-DMONO_ABLATE={g.get('ABLATE', 0)}",
+        *(["-DMONO_PROFILE"] if g.get("PROFILE") else []), *(["-DMONO_PLAIN_STORES"] if g.get("PLAIN_STORES") else []), f"-DMONO_ABLATE={g.get('ABLATE', 0)}",
         os.path.join(CSRC, "mono_kernel.cu"), "-o", out,
     ]
     r = subprocess.run(cmd, capture_output=True, text=True)

@@ -315,24 +315,24 @@ __device__ __forceinline__ void route_token(const float (&logit)[8], const float
     }
   }
 
-  uint32_t used = 0u;
+  // One 64-bit key per candidate, built once: orderable score in the high word, inverted expert id in
+  // the low word (ties fall to the lower id, and every key is unique). 0 = not selectable / taken.
+  unsigned long long key[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float v = sel[j] + 0.0f;  // folds -0 into +0 so that the integer key orders exactly like operator>
+    key[j] = (v > -FLT_MAX) ? ((static_cast<unsigned long long>(float_key(v)) << 32) |
+                               static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<uint32_t>(lane + 32 * j)))
+                            : 0ull;
+  }
   float wsum = 0.f;
   my_id = -1;
   my_w = 0.f;
 #pragma unroll 1
   for (int k = 0; k < TOP_K; ++k) {
-    unsigned long long best = 0ull;
+    unsigned long long best = key[0];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      // `+ 0.0f` folds -0 into +0 so that the integer key orders exactly like operator>.
-      const float v = sel[j] + 0.0f;
-      const bool ok = !((used >> j) & 1u) && (v > -FLT_MAX);
-      const unsigned long long key =
-          ok ? ((static_cast<unsigned long long>(float_key(v)) << 32) |
-                static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<uint32_t>(lane + 32 * j)))
-             : 0ull;
-      best = key > best ? key : best;
-    }
+    for (int j = 1; j < 8; ++j) best = key[j] > best ? key[j] : best;
     best = warp_max_u64(best);
     int bidx = -1;
     float wk = 0.f;
@@ -341,10 +341,13 @@ __device__ __forceinline__ void route_token(const float (&logit)[8], const float
       const int owner = bidx & 31, slot = bidx >> 5;
       float mine = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (j == slot) mine = unb[j];
+      for (int j = 0; j < 8; ++j) {
+        if (j == slot) {
+          mine = unb[j];
+          if (lane == owner) key[j] = 0ull;  // the owner retires the winner
+        }
+      }
       const float bu = __shfl_sync(0xFFFFFFFFu, mine, owner);
-      if (lane == owner) used |= 1u << slot;
       wk = (ROUTER_MODE == 0) ? __fdiv_rn(det_expf(bu - m), s) : bu;
     }
     wsum += wk;
@@ -1039,7 +1042,8 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
                   const float2 v = __fmul2_rn(acc[j * (WC / 2) + c * 8 + i], rw2);
                   w[i] = cvt_bf16x2_satfinite(v.x, v.y);
                 }
-                st_global_256(dst + c * 16, w);
+                // written once, read once by the slot sum: keep it from pushing expert weights out of L2
+                st_global_256_stream(dst + c * 16, w);
               }
             }
           }

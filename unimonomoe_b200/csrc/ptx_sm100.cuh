@@ -231,6 +231,17 @@ __device__ __forceinline__ void st_global_256(void* p, const uint32_t (&w)[8]) {
                : "memory");
 }
 
+// The same with the L2 evict-first priority, for data that is written once and read once much later.
+__device__ __forceinline__ void st_global_256_stream(void* p, const uint32_t (&w)[8]) {
+#ifdef MONO_PLAIN_STORES
+  st_global_256(p, w);
+#else
+  asm volatile("st.global.L2::evict_first.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(w[0]), "r"(w[1]),
+               "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+#endif
+}
+
 // ---------------------------------------------------------------- NVLS multimem
 // Sum of eight bf16 at the same offset on every rank of the multicast object, summed
 // in fp32 inside the switch and rounded once to bf16 (reference:
