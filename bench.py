@@ -200,6 +200,9 @@ def main() -> None:
     ap.add_argument("--parallel", default="auto", choices=["auto", "tp", "ep"],
                     help="N>1: tensor parallel (N=2,4) or expert parallel; auto = ep")
     ap.add_argument("--unfused", action="store_true", help="N>1: reduce with NCCL after the kernel instead of in-kernel")
+    ap.add_argument("--router", default="logits", choices=["logits", "gemv"],
+                    help="logits: the caller's router logits go in (the reference's interface); gemv: the bf16 gate "
+                         "weight goes in and the router linear runs inside the launch (no logits cross PCIe in e2e)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end leg, the library GEMM probe and the CPU baseline (profiling runs)")
     args = ap.parse_args()
@@ -263,13 +266,19 @@ def main() -> None:
         f"in-kernel NVLS multimem all-reduce, {plan.chunks_for(T)} chunks, {plan.ncomm} communication CTAs"
         if plan is not None else "NCCL all-reduce after the kernel")
 
+    rw16 = None
+    if args.router == "gemv":
+        if plan is not None:
+            raise SystemExit("--router gemv is wired for the unfused launch only: add --unfused")
+        rw16 = layer["router_w"].to(torch.bfloat16).contiguous()
+
     def launch(hs, lg):
         if plan is not None:
             plan.fused_tp_launch(hs, lg, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k,
                                  True, layer["bias"], expert_map=emap)
         else:
             mk.prefill_impl(hs, lg, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k, True,
-                            layer["bias"], out, expert_map=emap, scratch=sc)
+                            layer["bias"], out, expert_map=emap, scratch=sc, router_weight=rw16)
 
     def reduce_out():
         if world > 1 and plan is None:
@@ -316,8 +325,9 @@ def main() -> None:
     e2e_ms = None
     if not args.kernel_only:
         result = plan.pool.output(T) if plan is not None else out
-        e2e_ms = time_e2e(args, spec, batch, result, launch, reduce_out, world, dist, barrier, dev)
-    h2d = batch["hs"].numel() * 2 + batch["logits"].numel() * 4
+        e2e_ms = time_e2e(args, spec, batch, result, launch, reduce_out, world, dist, barrier, dev,
+                          with_logits=rw16 is None)
+    h2d = batch["hs"].numel() * 2 + (batch["logits"].numel() * 4 if rw16 is None else 0)
     d2h = out.numel() * 2
 
     if rank == 0:
@@ -328,7 +338,7 @@ def main() -> None:
         dist.destroy_process_group()
 
 
-def time_e2e(args, spec, batch, out, launch, reduce_out, world, dist, barrier, dev) -> float:
+def time_e2e(args, spec, batch, out, launch, reduce_out, world, dist, barrier, dev, with_logits=True) -> float:
     """End to end through the public API: host buffers in, host result out, copies inside the timed region."""
     T = batch["hs"].shape[0]
     hs_host = batch["hs"].cpu().pin_memory()
@@ -338,7 +348,8 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, dist, barrier, d
 
     def e2e_step():
         hs_dev.copy_(hs_host, non_blocking=True)
-        lg_dev.copy_(lg_host, non_blocking=True)
+        if with_logits:
+            lg_dev.copy_(lg_host, non_blocking=True)
         launch(hs_dev, lg_dev)
         reduce_out()
         out_host.copy_(out, non_blocking=True)
@@ -382,7 +393,9 @@ def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flop
         "config": {"workload": f"{spec.name} MoE layer prefill, T={T} tokens, H=2048, E=256, top-8, I=512, "
                                f"block-FP8 [128,128] weights", "tokens": T, "parallelism": par, "variant": variant,
                    "l2_policy": "inputs larger than L2: 805 MB of weights + 0.5 GB of partial rows stream per step",
-                   "reduce": reduce_desc},
+                   "reduce": reduce_desc,
+                   "router": ("bf16 router linear inside the launch (its 2*T*H*E FLOPs are not counted)"
+                              if args.router == "gemv" else "fp32 logits supplied by the caller")},
         "clocks": clk.summary(),
         "e2e": (None if e2e_ms is None else
                 {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,

@@ -148,6 +148,23 @@ int prefill_wgmma_shm_total(void);            /* Q:1789 */
 
 /* ---- additions of this library: no counterpart in the reference ---------------------- */
 
+/* The router linear inside the launch. The reference leaves it to the model (a separate GEMM before the
+ * hook, vllm_integration/vllm/_custom_ops.py:4618 takes finished logits). router_w_bf16 is the gate weight
+ * [E, K] in bf16; logits_out [T, E] fp32 receives the logits the kernel computed and routed on. The
+ * arguments from num_tokens on are those of launch_prefill_moe_wgmma_q1_ep2. Every CTA computes the
+ * logits of the tokens it routes itself (tcgen05.mma kind::f16, fp32 accumulation over ascending K slabs
+ * of 64), so no extra grid barrier is needed. -105: router_w_bf16 or logits_out is null. */
+int prefill_wgmma_has_router_gemv(void);      /* 1 = launch_prefill_moe_wgmma_q1_gemv is usable */
+int launch_prefill_moe_wgmma_q1_gemv(const void* router_w_bf16, float* logits_out, int num_tokens, int block_m,
+                                     void* workspace, size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
+                                     float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
+                                     const uint8_t* down_w_fp8, const float* down_w_scales, float* output_accum,
+                                     int32_t* topk_ids, float* topk_weights, int32_t* sorted_token_ids,
+                                     void* bf16_output, const float* router_bias, void* tp_mc, void* tp_pads,
+                                     int tp_rank, int tp_world, int tp_nchunk, int tp_ncomm, uint32_t tp_seq,
+                                     void* tp_seqctr, const void* tp_residual, float out_scale,
+                                     const int32_t* expert_map, prefill_mono_stream_t stream);
+
 int prefill_wgmma_arch(void);                 /* 100 = built for sm_100a */
 int prefill_wgmma_block_threads(void);        /* threads per CTA */
 int prefill_wgmma_stable_sort(void);          /* 1 = sorted_token_ids is deterministic (stable) */

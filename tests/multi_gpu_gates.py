@@ -12,6 +12,7 @@ Gates, per token count (all ranks must agree):
      with the same fold + multimem all-reduce                                    (tp8_fold_gate.py:332-409)
   5. back-to-back fused launches without a host sync, bitwise each time          (tp8_soak.py:306-318)
   6. a sentinel tail behind T*H in the pool slot is untouched                    (tp8_soak.py:511-536)
+  8. a captured fused launch replayed three times, bitwise each time            (tp8_soak.py:351-402)
   7. summed output against the CPU oracle on sampled tokens (rank 0)
 NVLS stays enabled: this test never kills a rank.
 """
@@ -122,6 +123,27 @@ def main():
             ok5 = ok5 and bool(torch.equal(out_pool.view(torch.int16), ref_symm.view(torch.int16)))
         mk.check_status(mk.scratch(T, dev)["workspace"])
         r["g5_back_to_back"] = ok5
+        # gate 8: a captured fused launch replayed three times; the device sequence counter advances on
+        # every replay, so the rank barriers never see a stale sequence (tp8_soak.py:351-402)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            plan.fused_tp_launch(*args_k, 8, True, layer["bias"])
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            plan.fused_tp_launch(*args_k, 8, True, layer["bias"])
+        ok8 = True
+        for _ in range(3):
+            out_pool.zero_()
+            dist.barrier()
+            graph.replay()
+            torch.cuda.synchronize()
+            ok8 = ok8 and bool(torch.equal(out_pool.view(torch.int16), ref_symm.view(torch.int16)))
+        mk.check_status(mk.scratch(T, dev)["workspace"])
+        r["g8_graph_replay"] = ok8
         # gate 6
         r["g6_tail_untouched"] = bool((tail == -7.0).all()) if tail.numel() else True
         # gate 4: fold

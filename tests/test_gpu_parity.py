@@ -270,3 +270,119 @@ def test_bounded_wait_reports_instead_of_hanging(gu, qwen_full):
     assert int(seqctr.item()) == 1
     res = gu.launch(mk, qwen_full, batch)
     assert torch.isfinite(res["out"].float()).all()
+
+
+def test_cuda_graph_capture_and_replay(gu, qwen_full):
+    """The launch is capturable (no allocation, no host synchronisation inside it): a captured launch
+    replayed three times, with fresh inputs copied into the captured buffers before each replay,
+    reproduces eager launches bit for bit (after validation/tp8_soak.py:351-402)."""
+    mk = gu.kernel("qwen_w1")
+    T = 1536
+    batches = [synth.make_batch(synth.QWEN, qwen_full, T, seed=20 + i, device=gu.DEV) for i in range(3)]
+    eager = []
+    for b in batches:
+        eager.append(gu.launch(mk, qwen_full, b, poison=False)["out"].clone())
+    hs = batches[0]["hs"].clone()
+    lg = batches[0]["logits"].clone()
+    out = torch.empty(T, 2048, dtype=torch.bfloat16, device=gu.DEV)
+    sc = mk.scratch(T, gu.DEV)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):   # warm-up on the capture stream, as torch asks
+        mk.prefill_impl(hs, lg, qwen_full["w13"], qwen_full["w13_scale"], qwen_full["w2"], qwen_full["w2_scale"], 8, True,
+                        None, out, scratch=sc)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        mk.prefill_impl(hs, lg, qwen_full["w13"], qwen_full["w13_scale"], qwen_full["w2"], qwen_full["w2_scale"], 8, True,
+                        None, out, scratch=sc)
+    for i, b in enumerate(batches):
+        hs.copy_(b["hs"])
+        lg.copy_(b["logits"])
+        out.fill_(float("nan"))
+        g.replay()
+        torch.cuda.synchronize()
+        mk.check_status(sc["workspace"])
+        assert torch.equal(out.view(torch.int16), eager[i].view(torch.int16)), i
+
+
+def _fp64_topk_margin(scores64, k=8):
+    """Gap between the k-th and (k+1)-th largest selection score of every token, in fp64."""
+    top = torch.topk(scores64, k + 1, dim=1).values
+    return (top[:, k - 1] - top[:, k])
+
+
+@pytest.mark.parametrize("T", [1, 1000, 16384])
+def test_router_linear_inside_the_launch(gu, oracle, qwen_full, T):
+    """The _gemv entry computes logits = x * W_r^T (bf16 operands, fp32 accumulation on the tensor cores)
+    for the tokens each CTA routes and routes on them in the same launch. Its accumulation order inside
+    one instruction is the hardware's, so the logits are compared with an fp64 linear within a tolerance,
+    and routing is pinned in two steps: (1) ids, weights, counts and the permutation are bit-exact against
+    the oracle fed with the logits the kernel itself produced; (2) every token whose expert set differs
+    from an fp64 route sits at a decision margin below 1e-5 (the rule of research_archive/ds3_acc.py:440-458).
+    The output then has to equal, bit for bit, a logits-in launch on those same logits."""
+    mk = gu.kernel("qwen_w1")
+    assert mk.has_gemv
+    from unimonomoe_b200.loader import prepare_router_weight
+    batch = synth.make_batch(synth.QWEN, qwen_full, T, seed=3, device=gu.DEV)
+    rw16 = prepare_router_weight(qwen_full["router_w"].to(torch.bfloat16))
+    out = torch.full((T, 2048), float("nan"), dtype=torch.bfloat16, device=gu.DEV)
+    sc = mk.scratch(T, gu.DEV)
+    sc.pop("logits", None)
+    mk.prefill_impl(batch["hs"], None, qwen_full["w13"], qwen_full["w13_scale"], qwen_full["w2"], qwen_full["w2_scale"],
+                    8, True, None, out, check=True, router_weight=rw16)
+    lk = sc["logits"].clone()
+    ids_k, w_k, srt_k = sc["topk_ids"].cpu().numpy(), sc["topk_weights"].cpu().numpy(), sc["sorted_ids"].cpu().numpy()
+    wv = mk.workspace_view(sc["workspace"])
+    # logits against fp64
+    ref64 = batch["hs"].double() @ rw16.double().t()
+    err = float((lk.double() - ref64).abs().max())
+    assert err <= 4e-5, err   # measured 1.2e-5 at |logit| up to 5.4: the accumulator keeps a little less than fp32
+    # (1) routing of the kernel's own logits, bit-exact
+    ids, w, _ = oracle.route(lk, mode=0)
+    assert (ids_k == ids).all() and (w_k.view(np.uint32) == w.view(np.uint32)).all()
+    cnt, off, srt = oracle.sort_slots(ids, 256)
+    assert (wv["expert_counts"].numpy()[:256] == cnt).all() and (srt_k[:len(srt)] == srt).all()
+    # (2) disagreements with an fp64 route only at sub-epsilon margins
+    ids64 = torch.topk(ref64, 8, dim=1).indices.sort(1).values.cpu().numpy()
+    differ = (np.sort(ids_k, 1) != ids64).any(1)
+    if differ.any():
+        # the reference's bound is 1e-5 on sigmoid scores in [0, 1]; softmax selection compares raw logits of
+        # magnitude ~5, and two logits that are each off by `err` can swap only when they are closer than 2*err
+        marg = _fp64_topk_margin(ref64).cpu().numpy()
+        assert float(marg[differ].max()) <= 2 * err, (int(differ.sum()), float(marg[differ].max()), err)
+    assert differ.sum() <= max(2, T // 2000)
+    # same output as the logits-in entry on those logits
+    b2 = {"hs": batch["hs"], "logits": lk}
+    res = gu.launch(mk, qwen_full, b2, poison=False)
+    assert torch.equal(res["out"].view(torch.int16), out.view(torch.int16))
+
+
+def test_tiny_batches_repeated(gu, qwen_full):
+    """At one or a few tokens almost every CTA has no tile and runs straight through the expert phase:
+    the hand-back of registers between producer and epilogue warps must not depend on who asks first.
+    150 launches each of 1 and 7 tokens, through both entries, with a host-side deadline instead of a
+    blocking synchronise so that a stall fails the test."""
+    import time
+    mk = gu.kernel("qwen_w1")
+    from unimonomoe_b200.loader import prepare_router_weight
+    rw16 = prepare_router_weight(qwen_full["router_w"].to(torch.bfloat16))
+    for T in (1, 7):
+        batch = synth.make_batch(synth.QWEN, qwen_full, T, seed=11, device=gu.DEV)
+        out = torch.empty(T, 2048, dtype=torch.bfloat16, device=gu.DEV)
+        first = None
+        for i in range(150):
+            ev = torch.cuda.Event()
+            mk.prefill_impl(batch["hs"], batch["logits"], qwen_full["w13"], qwen_full["w13_scale"], qwen_full["w2"],
+                            qwen_full["w2_scale"], 8, True, None, out, router_weight=rw16 if i % 2 else None)
+            ev.record()
+            t0 = time.time()
+            while not ev.query():
+                assert time.time() - t0 < 10.0, f"launch {i} at T={T} did not finish within 10 s"
+                time.sleep(0.001)
+            if i % 2 == 0:
+                if first is None:
+                    first = out.clone()
+                assert torch.equal(out.view(torch.int16), first.view(torch.int16))
+        mk.check_status(mk.scratch(T, gu.DEV)["workspace"])

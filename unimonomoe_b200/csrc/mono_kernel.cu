@@ -1,6 +1,8 @@
 // Single-launch FP8 MoE prefill layer for B200 (sm_100a): one persistent kernel, 148
 // CTAs (one per SM), phases separated by bounded software grid barriers.
 //
+//   phase R   (only through the _gemv entry) router logits = x * W_r^T on the tensor cores:
+//             bf16 x bf16 -> fp32, every CTA for the tokens it routes itself
 //   phase 0   router top-k from fp32 logits (softmax, sigmoid+bias, or group-limited
 //             sigmoid+bias), per-warp expert histograms; bf16 -> e4m3 activation
 //             quantisation with one fp32 scale per (token, 128 columns)
@@ -174,10 +176,15 @@ static_assert(REGS_LAUNCH * BLOCK <= 65536, "launch register count exceeds the r
 
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t IDESC = umma_idesc_e4m3_f32(128, BC);
+// router GEMV: one [128 tokens x 256 experts] accumulator, K slabs of 64 bf16 (128 bytes)
+constexpr uint32_t IDESC_ROUTER = umma_idesc_bf16_f32(128, E);
+constexpr int RK = K_DIM / 64;
+constexpr int RS = (SA < SB) ? SA : SB;
 
 // wait sites reported in the status word
 enum Site : uint32_t {
   kSiteEmptyB = 1, kSiteFullB, kSiteFullA, kSiteEmptyA, kSiteTmemEmpty, kSiteTmemFull, kSiteInterReady,
+  kSiteRouterEmpty, kSiteRouterFull, kSiteRouterAccEmpty, kSiteRouterAccFull,
 };
 
 struct Params {
@@ -209,8 +216,12 @@ struct Params {
   float* dbg_acc;
   uint8_t* dbg_inter;
   float* dbg_inter_scale;
+  // router GEMV (null: the caller supplied the logits)
+  float* logits_out;        // [T, E] fp32, written by phase R and read back by phase 0
   alignas(64) CUtensorMap tm_up;
   alignas(64) CUtensorMap tm_down;
+  alignas(64) CUtensorMap tm_x;    // bf16 activations [T, K]
+  alignas(64) CUtensorMap tm_rw;   // bf16 router weight [E, K]
 };
 
 struct TileInfo {
@@ -414,6 +425,7 @@ struct __align__(16) SharedState {
   uint64_t fullA[4], emptyA[4], fullB[4], emptyB[4];
   uint64_t tmem_full[NBUF], tmem_empty[NBUF];
   uint64_t inter_ready;
+  uint64_t rfull[4], rempty[4], racc_full, racc_empty;  // phase R only
   uint32_t tmem_base;
   uint32_t flag;          // grid_sync result broadcast
   int n_my_tiles;
@@ -461,23 +473,126 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
     atomicExch(&ws->tp_seq_pub, sq);
   }
 
-  // ================================================================ phase 0
-  for (int i = tid; i < NWARPS * E; i += BLOCK) hist[i] = 0;
-  __syncthreads();
-
-  // Every warp first routes its contiguous range of tokens, then quantises activations. (Splitting the
-  // warps into routers and quantisers was measured and is slower: routing is instruction-bound and
-  // wants all twelve warps.)
+  // Every warp routes a contiguous range of tokens, so a CTA routes one contiguous range as well.
   const int gwarp = bid * NWARPS + warp;
   const int nwarps_grid = kGrid * NWARPS;
   const int tok_per_warp = (T + nwarps_grid - 1) / nwarps_grid;
   const int t_begin = min(T, gwarp * tok_per_warp);
   const int t_end = min(T, t_begin + tok_per_warp);
 
+  // ================================================================ phase R (router GEMV)
+  // logits[t, e] = sum_k x[t, k] * W_r[e, k] for the tokens THIS CTA routes in phase 0, so no grid
+  // barrier separates the two. bf16 products are exact in fp32; the accumulation runs in the tensor
+  // core's fp32 accumulator over K slabs of 64 in ascending order (its order inside one instruction is
+  // the hardware's). One accumulator of 128 tokens x 256 experts in tensor memory; TMA brings one
+  // [128 x 64] slab of x and one [256 x 64] slab of W_r per stage, both in the 128-byte swizzle.
+  const bool gemv = p.logits_out != nullptr;
+  if (gemv) {
+    if (tid == 0) {
+      for (int s = 0; s < RS; ++s) { mbar_init(&S.rfull[s], 1); mbar_init(&S.rempty[s], 1); }
+      mbar_init(&S.racc_full, 1);
+      mbar_init(&S.racc_empty, N_EPI / 32);
+      mbar_init_fence();
+    }
+    if (warp == WARP_MMA) {
+      tmem_alloc(&S.tmem_base, TMEM_COLS);
+      tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_r = S.tmem_base;
+    const int c0 = min(T, bid * NWARPS * tok_per_warp);
+    const int c1 = min(T, c0 + NWARPS * tok_per_warp);
+    const int n_rt = (c1 - c0 + TILE_M - 1) / TILE_M;
+    if (warp == WARP_TMA) {
+      if (lane == 0) {
+        tma_prefetch_desc(&p.tm_x);
+        tma_prefetch_desc(&p.tm_rw);
+        uint32_t n = 0;
+        bool ok = true;
+        for (int rt = 0; rt < n_rt && ok; ++rt) {
+          for (int ks = 0; ks < RK; ++ks, ++n) {
+            const uint32_t st = n % RS;
+            if (!mbar_wait(&S.rempty[st], ((n / RS) & 1u) ^ 1u, wc, kSiteRouterEmpty)) { ok = false; break; }
+            mbar_arrive_expect_tx(&S.rfull[st], A_STAGE_BYTES + B_STAGE_BYTES);
+            tma_load_2d(&p.tm_x, static_cast<uint32_t>(ks * 64), static_cast<uint32_t>(c0 + rt * TILE_M),
+                        a_ring + st * A_STAGE_BYTES, &S.rfull[st]);
+            tma_load_2d(&p.tm_rw, static_cast<uint32_t>(ks * 64), 0u, b_ring + st * B_STAGE_BYTES, &S.rfull[st]);
+          }
+        }
+      }
+    } else if (warp == WARP_MMA) {
+      if (lane == 0) {
+        const uint32_t a_u32 = smem_u32(a_ring), b_u32 = smem_u32(b_ring);
+        uint32_t n = 0;
+        bool ok = true;
+        for (int rt = 0; rt < n_rt && ok; ++rt) {
+          if (!mbar_wait(&S.racc_empty, (static_cast<uint32_t>(rt) & 1u) ^ 1u, wc, kSiteRouterAccEmpty)) break;
+          tc_fence_after();
+          for (int ks = 0; ks < RK; ++ks, ++n) {
+            const uint32_t st = n % RS;
+            if (!mbar_wait(&S.rfull[st], (n / RS) & 1u, wc, kSiteRouterFull)) { ok = false; break; }
+            tc_fence_after();
+            const uint64_t da = umma_desc_sw128(a_u32 + st * A_STAGE_BYTES);
+            const uint64_t db = umma_desc_sw128(b_u32 + st * B_STAGE_BYTES);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) umma_bf16(tmem_r, da + 2u * k, db + 2u * k, IDESC_ROUTER, (ks | k) ? 1u : 0u);
+            umma_commit(&S.rempty[st]);
+          }
+          if (ok) umma_commit(&S.racc_full);
+        }
+      }
+    } else if (warp >= 4) {
+      const int et = tid - 128;
+      const int h = et >> 7;        // which 128 experts (EPI_WGS == 2), or which 64 (EPI_WGS == 4)
+      const int q = warp & 3;
+      const int r = q * 32 + lane;
+      constexpr int RCOLS = E / EPI_WGS;
+      const uint32_t t_lane = tmem_r + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(h * RCOLS);
+      for (int rt = 0; rt < n_rt; ++rt) {
+        if (!mbar_wait(&S.racc_full, static_cast<uint32_t>(rt) & 1u, wc, kSiteRouterAccFull)) break;
+        tc_fence_after();
+        const int row = c0 + rt * TILE_M + r;
+#pragma unroll
+        for (int c = 0; c < RCOLS / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_n<32>(t_lane + c * 32, v);
+          tmem_ld_wait();
+          if (row < c1) {
+            float* dst = p.logits_out + static_cast<size_t>(row) * E + h * RCOLS + c * 32;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t w8[8] = {v[8 * i], v[8 * i + 1], v[8 * i + 2], v[8 * i + 3],
+                                      v[8 * i + 4], v[8 * i + 5], v[8 * i + 6], v[8 * i + 7]};
+              st_global_256(dst + 8 * i, w8);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&S.racc_empty);
+      }
+    }
+    // the logits this CTA wrote are read back by its own warps below; the operand rings are reused
+    tc_fence_before();
+    __syncthreads();
+    if (bid == 0 && tid == 0) ws->phase_ns[5] = globaltimer_ns();
+  }
+  const float* lg_src = gemv ? p.logits_out : p.logits;
+
+  // ================================================================ phase 0
+  for (int i = tid; i < NWARPS * E; i += BLOCK) hist[i] = 0;
+  __syncthreads();
+
+  // Every warp first routes its range of tokens, then quantises activations. (Splitting the
+  // warps into routers and quantisers was measured and is slower: routing is instruction-bound and
+  // wants all twelve warps.)
+
   float lg_next[8];
   if (t_begin < t_end) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) lg_next[j] = p.logits[static_cast<size_t>(t_begin) * E + lane + 32 * j];
+    for (int j = 0; j < 8; ++j) lg_next[j] = lg_src[static_cast<size_t>(t_begin) * E + lane + 32 * j];
   }
   for (int t = t_begin; t < t_end; ++t) {
     int my_id;
@@ -487,7 +602,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
     for (int j = 0; j < 8; ++j) lg[j] = lg_next[j];
     if (t + 1 < t_end) {  // the next token's logits are in flight while this one is routed
 #pragma unroll
-      for (int j = 0; j < 8; ++j) lg_next[j] = p.logits[static_cast<size_t>(t + 1) * E + lane + 32 * j];
+      for (int j = 0; j < 8; ++j) lg_next[j] = lg_src[static_cast<size_t>(t + 1) * E + lane + 32 * j];
     }
     route_token(lg, p.router_bias, lane, my_id, my_w);
     if (lane < TOP_K) {
@@ -614,7 +729,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
     mbar_init(&S.inter_ready, N_EPI / 32);
     mbar_init_fence();
   }
-  if (warp == WARP_MMA) {
+  if (warp == WARP_MMA && !gemv) {  // phase R already holds the allocation
     tmem_alloc(&S.tmem_base, TMEM_COLS);
     tmem_relinquish();
   }
@@ -801,8 +916,6 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       cp_async_wait<0>();
       if (gt == 0) { PROF_STORE(6, pg_emptyA); }
     }
-    __syncwarp();
-    reg_inc<REGS_LAUNCH>();
   } else {
     // ------------------------------------------------------------ epilogue (EPI_WGS x 128 threads)
     reg_inc<REGS_EPILOGUE>();
@@ -1059,13 +1172,17 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
 #endif
       }
     }
-    reg_dec<REGS_LAUNCH>();
   }
 
   // teardown of phase 2: when aborting, give in-flight bulk copies and MMAs time to land
   if (aborted(ws)) __nanosleep(200000);
   tc_fence_before();
   __syncthreads();
+  // Registers go back to the launch split only now, behind the barrier. If the producer warps asked
+  // for theirs back right after their own loops (a CTA without tiles reaches that point at once), they
+  // could take back what they had just released before the epilogue warps were served, and the
+  // epilogue's setmaxnreg.inc would then wait for registers that nobody releases any more.
+  if (warp < 4) reg_inc<REGS_LAUNCH>(); else reg_dec<REGS_LAUNCH>();
   if (warp == WARP_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
@@ -1255,6 +1372,21 @@ int make_u8_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, 
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// 2-D bf16 tensor [rows, cols] row-major, box box_rows x 64 elements (128 bytes), 128-byte swizzle;
+// rows past the end read as zero.
+int make_bf16_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t gd[2] = {cols, rows};
+  cuuint64_t gs[1] = {cols * 2};
+  cuuint32_t bx[2] = {64u, box_rows};
+  cuuint32_t es[2] = {1u, 1u};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gd, gs, bx, es,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 }  // namespace
 }  // namespace mono
 
@@ -1314,7 +1446,10 @@ void prefill_wgmma_set_debug(void* acc, void* inter, void* inter_scale) {
   g_dbg_inter_scale = static_cast<float*>(inter_scale);
 }
 
-int launch_prefill_moe_wgmma_q1_ep2(const float* logits, int num_tokens, int block_m, void* workspace,
+// Common launcher. router_w == nullptr: `logits` holds the caller's router logits. Otherwise
+// router_w is the bf16 router weight [E, K] and `logits` is the [T, E] fp32 buffer the kernel fills.
+static int launch_common(const void* router_w, float* logits_buf, const float* logits, int num_tokens, int block_m,
+                         void* workspace,
                                     size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
                                     float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
                                     const uint8_t* down_w_fp8, const float* down_w_scales, float* output_accum,
@@ -1324,6 +1459,7 @@ int launch_prefill_moe_wgmma_q1_ep2(const float* logits, int num_tokens, int blo
                                     void* tp_seqctr, const void* tp_residual, float out_scale,
                                     const int32_t* expert_map, cudaStream_t stream) {
   (void)block_m;  // the tile height is the compiled TILE_M
+  if (router_w != nullptr) logits = logits_buf;
   if (EP_BUILD && expert_map == nullptr) return -120;
   if (!EP_BUILD && expert_map != nullptr) return -121;
   if (workspace == nullptr || workspace_bytes < sizeof(Workspace)) return -100;
@@ -1392,7 +1528,15 @@ int launch_prefill_moe_wgmma_q1_ep2(const float* logits, int num_tokens, int blo
     fprintf(stderr, "down-projection tensor map failed: %d\n", rc);
     return -3;
   }
-
+  if (router_w != nullptr) {
+    p.logits_out = logits_buf;
+    rc = make_bf16_map(&p.tm_x, act_bf16, static_cast<uint64_t>(num_tokens), K_DIM, TILE_M);
+    if (rc == 0) rc = make_bf16_map(&p.tm_rw, router_w, E, K_DIM, E);
+    if (rc != 0) {
+      fprintf(stderr, "router tensor map failed: %d\n", rc);
+      return -4;
+    }
+  }
 
   err = cudaFuncSetAttribute(moe_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM);
   if (err != cudaSuccess) return static_cast<int>(err);
@@ -1406,6 +1550,42 @@ int launch_prefill_moe_wgmma_q1_ep2(const float* logits, int num_tokens, int blo
     return static_cast<int>(err);
   }
   return 0;
+}
+
+int launch_prefill_moe_wgmma_q1_ep2(const float* logits, int num_tokens, int block_m, void* workspace,
+                                    size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
+                                    float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
+                                    const uint8_t* down_w_fp8, const float* down_w_scales, float* output_accum,
+                                    int32_t* topk_ids, float* topk_weights, int32_t* sorted_token_ids,
+                                    void* bf16_output, const float* router_bias, void* tp_mc, void* tp_pads,
+                                    int tp_rank, int tp_world, int tp_nchunk, int tp_ncomm, uint32_t tp_seq,
+                                    void* tp_seqctr, const void* tp_residual, float out_scale,
+                                    const int32_t* expert_map, cudaStream_t stream) {
+  return launch_common(nullptr, nullptr, logits, num_tokens, block_m, workspace, workspace_bytes, act_bf16, act_fp8,
+                       act_scales, up_w_fp8, up_w_scales, down_w_fp8, down_w_scales, output_accum, topk_ids,
+                       topk_weights, sorted_token_ids, bf16_output, router_bias, tp_mc, tp_pads, tp_rank, tp_world,
+                       tp_nchunk, tp_ncomm, tp_seq, tp_seqctr, tp_residual, out_scale, expert_map, stream);
+}
+
+// The router linear inside the launch: router_w_bf16 is the gate weight [E, K] in bf16 (the checkpoints
+// of both model families store it so) and logits_out a [T, E] fp32 buffer that receives the logits the
+// kernel routed on. Everything from num_tokens on is the argument list of the _ep2 entry.
+// -105: router_w_bf16 or logits_out is null.
+int prefill_wgmma_has_router_gemv() { return 1; }
+int launch_prefill_moe_wgmma_q1_gemv(const void* router_w_bf16, float* logits_out, int num_tokens, int block_m,
+                                     void* workspace, size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
+                                     float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
+                                     const uint8_t* down_w_fp8, const float* down_w_scales, float* output_accum,
+                                     int32_t* topk_ids, float* topk_weights, int32_t* sorted_token_ids,
+                                     void* bf16_output, const float* router_bias, void* tp_mc, void* tp_pads,
+                                     int tp_rank, int tp_world, int tp_nchunk, int tp_ncomm, uint32_t tp_seq,
+                                     void* tp_seqctr, const void* tp_residual, float out_scale,
+                                     const int32_t* expert_map, cudaStream_t stream) {
+  if (router_w_bf16 == nullptr || logits_out == nullptr) return -105;
+  return launch_common(router_w_bf16, logits_out, nullptr, num_tokens, block_m, workspace, workspace_bytes, act_bf16,
+                       act_fp8, act_scales, up_w_fp8, up_w_scales, down_w_fp8, down_w_scales, output_accum, topk_ids,
+                       topk_weights, sorted_token_ids, bf16_output, router_bias, tp_mc, tp_pads, tp_rank, tp_world,
+                       tp_nchunk, tp_ncomm, tp_seq, tp_seqctr, tp_residual, out_scale, expert_map, stream);
 }
 
 int launch_prefill_moe_wgmma_q1_tp2(const float* logits, int num_tokens, int block_m, void* workspace,

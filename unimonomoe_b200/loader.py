@@ -44,6 +44,19 @@ def variant_path(variant: str) -> str:
     return os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", f"libprefill_mono_{variant}.so")
 
 
+def prepare_router_weight(weight: torch.Tensor) -> torch.Tensor:
+    """The gate weight [E, K] as the in-kernel router wants it: contiguous bfloat16. Done once when the
+    layer is loaded, never per call. The checkpoints of both model families store the gate in bf16 and
+    the fp32 router linear of the DeepSeek harness upcasts it (validation/ds3_acc.py:412), so the
+    conversion is exact; a weight that does not survive the round trip is refused, because the kernel
+    would then route on different logits than the caller's own linear."""
+    w16 = weight.to(torch.bfloat16).contiguous()
+    if weight.dtype != torch.bfloat16 and not torch.equal(w16.to(weight.dtype), weight):
+        raise ValueError("router weight is not exactly representable in bfloat16; keep the router linear outside "
+                         "the kernel and pass logits")
+    return w16
+
+
 class MonoKernel:
     """One loaded ``libprefill_mono_*.so``."""
 
@@ -64,6 +77,7 @@ class MonoKernel:
         self.has_tp = self._bind("launch_prefill_moe_wgmma_q1_tp")
         self.has_tp2 = self._bind("launch_prefill_moe_wgmma_q1_tp2")
         self.has_ep = self._bind("launch_prefill_moe_wgmma_q1_ep")
+        self.has_gemv = self._bind("launch_prefill_moe_wgmma_q1_gemv") and bool(self._int_symbol("has_router_gemv"))
         self._caps = {}
         for name in _TP_CAP_SYMBOLS:
             self._caps[name] = self._int_symbol(name)
@@ -229,9 +243,13 @@ class MonoKernel:
     # ------------------------------------------------------------------ launch
     def prefill_impl(self, activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
                      expert_scales_down, top_k, renormalize, e_score_correction_bias, out, tp=None, residual=None,
-                     out_scale=1.0, expert_map=None, scratch=None, check=False) -> dict:
+                     out_scale=1.0, expert_map=None, scratch=None, check=False, router_weight=None) -> dict:
         """Launch the kernel into ``out`` (_custom_ops.py:4568-4762). Returns the scratch dict
-        (topk_ids, topk_weights, sorted_ids, workspace, ...) the launch wrote."""
+        (topk_ids, topk_weights, sorted_ids, workspace, ...) the launch wrote.
+
+        With ``router_weight`` (the gate weight [E, K] in bf16, see `prepare_router_weight`) the router
+        linear runs inside the launch; ``router_logits`` is then ignored and may be None, and the logits
+        the kernel routed on are left in ``scratch["logits"]``."""
         if not torch.cuda.is_available() or not activations_in.is_cuda:
             raise RuntimeError("the FP8 MoE prefill kernel needs a CUDA device; there is no CPU path")
         M, K = activations_in.shape
@@ -244,7 +262,18 @@ class MonoKernel:
         act = activations_in.contiguous()
         if act.dtype != torch.bfloat16:
             raise RuntimeError(f"monokernel activations must be bfloat16, got {act.dtype}")
-        logits = router_logits.float().contiguous()
+        rw = None
+        if router_weight is not None:
+            if not self.has_gemv:
+                raise RuntimeError("loaded monokernel .so has no launch_prefill_moe_wgmma_q1_gemv")
+            rw = router_weight
+            E = self.geometry()["num_experts"]
+            if rw.dtype != torch.bfloat16 or tuple(rw.shape) != (E, K) or not rw.is_contiguous() or rw.device != device:
+                raise RuntimeError(f"in-kernel router needs a contiguous bfloat16 [{E}, {K}] gate weight on {device}, got "
+                                   f"{tuple(rw.shape)} {rw.dtype} on {rw.device}; convert once with prepare_router_weight")
+            logits = None
+        else:
+            logits = router_logits.float().contiguous()
         w_up = expert_weights_up.contiguous().view(torch.uint8)
         w_down = expert_weights_down.contiguous().view(torch.uint8)
         s_up = expert_scales_up.float().contiguous()
@@ -286,8 +315,14 @@ class MonoKernel:
 
         sc = scratch if scratch is not None else self.scratch(M, device)
         vp = ctypes.c_void_p
-        args = [
-            vp(logits.data_ptr()), ctypes.c_int(M), ctypes.c_int(128),
+        if rw is not None:
+            if "logits" not in sc:
+                sc["logits"] = torch.empty(M, rw.size(0), dtype=torch.float32, device=device)
+            head = [vp(rw.data_ptr()), vp(sc["logits"].data_ptr())]
+        else:
+            head = [vp(logits.data_ptr())]
+        args = head + [
+            ctypes.c_int(M), ctypes.c_int(128),
             vp(sc["workspace"].data_ptr()), ctypes.c_size_t(sc["workspace"].numel()),
             vp(act.data_ptr()), vp(sc["act_fp8"].data_ptr()), vp(sc["act_scales"].data_ptr()),
             vp(w_up.data_ptr()), vp(s_up.data_ptr()), vp(w_down.data_ptr()), vp(s_down.data_ptr()),
@@ -295,7 +330,14 @@ class MonoKernel:
             vp(sc["sorted_ids"].data_ptr()), vp(out.data_ptr()),
         ]
         bias_arg = vp(bias.data_ptr() if bias is not None else 0)
-        if tp is not None:
+        if rw is not None:
+            # one entry point carries every option: absent ones are passed as null / neutral values
+            mc, pads, seqctr, rank, world, nchunk, ncomm = tp if tp is not None else (0, 0, 0, 0, 1, 1, 0)
+            entry = self.lib.launch_prefill_moe_wgmma_q1_gemv
+            args += [bias_arg, vp(int(mc)), vp(int(pads)), ctypes.c_int(int(rank)), ctypes.c_int(int(world)),
+                     ctypes.c_int(int(nchunk)), ctypes.c_int(int(ncomm)), ctypes.c_uint(0), vp(int(seqctr)),
+                     vp(int(resid_ptr)), ctypes.c_float(float(out_scale)), vp(emap.data_ptr() if emap is not None else 0)]
+        elif tp is not None:
             mc, pads, seqctr, rank, world, nchunk, ncomm = tp
             args += [bias_arg, vp(int(mc)), vp(int(pads)), ctypes.c_int(int(rank)), ctypes.c_int(int(world)),
                      ctypes.c_int(int(nchunk)), ctypes.c_int(int(ncomm)), ctypes.c_uint(0), vp(int(seqctr))]
@@ -323,26 +365,26 @@ class MonoKernel:
         if rc != 0:
             raise RuntimeError(f"launch_prefill_moe_wgmma_q1 failed: rc={rc}")
         # keep the converted inputs alive until the stream has consumed them
-        sc["_keepalive"] = (act, logits, w_up, w_down, s_up, s_down, bias, emap)
+        sc["_keepalive"] = (act, logits, rw, w_up, w_down, s_up, s_down, bias, emap)
         if check:
             self.check_status(sc["workspace"])
         return sc
 
     def prefill(self, activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
                 expert_scales_down, top_k=8, renormalize=True, e_score_correction_bias=None, expert_map=None,
-                check=False) -> torch.Tensor:
+                check=False, router_weight=None) -> torch.Tensor:
         """Allocating variant (_custom_ops.py:4820-4858). Under EP the result is this rank's partial sum."""
         M, H = activations_in.size(0), expert_weights_down.size(1)
         out = torch.empty(M, H, dtype=torch.bfloat16, device=activations_in.device)
         self.prefill_impl(activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
                           expert_scales_down, top_k, renormalize, e_score_correction_bias, out, None, None, 1.0,
-                          expert_map, check=check)
+                          expert_map, check=check, router_weight=router_weight)
         return out
 
     def prefill_out(self, activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
                     expert_scales_down, out, top_k=8, renormalize=True, e_score_correction_bias=None, tp_mc_ptr=0,
                     tp_pads_ptr=0, tp_seqctr_ptr=0, tp_rank=0, tp_world=1, tp_nchunk=0, tp_ncomm=0, tp_residual=None,
-                    tp_out_scale=1.0, check=False, expert_map=None) -> None:
+                    tp_out_scale=1.0, check=False, expert_map=None, router_weight=None) -> None:
         """Write into a caller-supplied destination (_custom_ops.py:4861-4924). tp_ncomm > 0 selects the
         fused collective, in which case ``out`` must be the symmetric window tp_mc_ptr aliases."""
         tp = None
@@ -352,7 +394,7 @@ class MonoKernel:
             tp = (tp_mc_ptr, tp_pads_ptr, tp_seqctr_ptr, tp_rank, tp_world, tp_nchunk, tp_ncomm)
         self.prefill_impl(activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
                           expert_scales_down, top_k, renormalize, e_score_correction_bias, out, tp, tp_residual,
-                          tp_out_scale, expert_map, check=check)
+                          tp_out_scale, expert_map, check=check, router_weight=router_weight)
 
 
 # ---------------------------------------------------------------------- module-level mirror
