@@ -272,13 +272,13 @@ def main() -> None:
             raise SystemExit("--router gemv is wired for the unfused launch only: add --unfused")
         rw16 = layer["router_w"].to(torch.bfloat16).contiguous()
 
-    def launch(hs, lg):
+    def launch(hs, lg, dst=None):
         if plan is not None:
             plan.fused_tp_launch(hs, lg, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k,
                                  True, layer["bias"], expert_map=emap)
         else:
             mk.prefill_impl(hs, lg, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k, True,
-                            layer["bias"], out, expert_map=emap, scratch=sc, router_weight=rw16)
+                            layer["bias"], out if dst is None else dst, expert_map=emap, scratch=sc, router_weight=rw16)
 
     def reduce_out():
         if world > 1 and plan is None:
@@ -325,8 +325,11 @@ def main() -> None:
     e2e_ms = None
     if not args.kernel_only:
         result = plan.pool.output(T) if plan is not None else out
+        # a second output slot lets the next kernel run while the previous result is still going to the host;
+        # the fused reduce writes the one symmetric pool slot, and NCCL reduces `out` in place
+        second = torch.empty_like(out) if world == 1 else None
         e2e_ms = time_e2e(args, spec, batch, result, launch, reduce_out, world, dist, barrier, dev,
-                          with_logits=rw16 is None)
+                          with_logits=rw16 is None, second_out=second)
     h2d = batch["hs"].numel() * 2 + (batch["logits"].numel() * 4 if rw16 is None else 0)
     d2h = out.numel() * 2
 
@@ -338,36 +341,82 @@ def main() -> None:
         dist.destroy_process_group()
 
 
-def time_e2e(args, spec, batch, out, launch, reduce_out, world, dist, barrier, dev, with_logits=True) -> float:
-    """End to end through the public API: host buffers in, host result out, copies inside the timed region."""
+def time_e2e(args, spec, batch, out, launch, reduce_out, world, dist, barrier, dev, with_logits=True,
+             second_out=None) -> tuple:
+    """End to end through the public API: host buffers in, host result out, every step's copies inside the
+    timed region. Returns (ms per step with the steps software-pipelined, ms per step strictly serial).
+
+    Pipelined: the upload of step i+1, the kernel of step i and the download of step i-1 run on three
+    streams over two input slots (and two output slots when `second_out` is given; with one output slot the
+    next kernel waits for the download). Every step still moves its own inputs and its own result."""
     T = batch["hs"].shape[0]
     hs_host = batch["hs"].cpu().pin_memory()
     lg_host = batch["logits"].cpu().pin_memory()
-    out_host = torch.empty(T, spec.hidden, dtype=torch.bfloat16).pin_memory()
-    hs_dev, lg_dev = torch.empty_like(batch["hs"]), torch.empty_like(batch["logits"])
+    outs = [out] if second_out is None else [out, second_out]
+    out_host = [torch.empty(T, spec.hidden, dtype=torch.bfloat16).pin_memory() for _ in outs]
+    NB = 2
+    hs_dev = [torch.empty_like(batch["hs"]) for _ in range(NB)]
+    lg_dev = [torch.empty_like(batch["logits"]) for _ in range(NB)]
+    cur = torch.cuda.current_stream()
+    s_in, s_c, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(NB)]     # upload of the slot finished
+    ev_k = [torch.cuda.Event() for _ in range(NB)]      # the kernel that read the slot finished
+    ev_o = [torch.cuda.Event() for _ in outs]           # download of the output slot finished
 
-    def e2e_step():
-        hs_dev.copy_(hs_host, non_blocking=True)
+    def serial_step():
+        hs_dev[0].copy_(hs_host, non_blocking=True)
         if with_logits:
-            lg_dev.copy_(lg_host, non_blocking=True)
-        launch(hs_dev, lg_dev)
+            lg_dev[0].copy_(lg_host, non_blocking=True)
+        launch(hs_dev[0], lg_dev[0], outs[0])
         reduce_out()
-        out_host.copy_(out, non_blocking=True)
+        out_host[0].copy_(outs[0], non_blocking=True)
 
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    n_e2e = max(5, min(args.steps, 20))
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record()
-    for _ in range(n_e2e):
-        e2e_step()
-    e3.record()
-    barrier()
-    t = torch.tensor([e2.elapsed_time(e3) / n_e2e], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t[0])
+    def piped_step(i):
+        b, o = i % NB, i % len(outs)
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_k[b])
+            hs_dev[b].copy_(hs_host, non_blocking=True)
+            if with_logits:
+                lg_dev[b].copy_(lg_host, non_blocking=True)
+            ev_in[b].record(s_in)
+        with torch.cuda.stream(s_c):
+            s_c.wait_event(ev_in[b])
+            s_c.wait_event(ev_o[o])
+            launch(hs_dev[b], lg_dev[b], outs[o])
+            reduce_out()
+            ev_k[b].record(s_c)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_k[b])
+            out_host[o].copy_(outs[o], non_blocking=True)
+            ev_o[o].record(s_out)
+
+    def timed(fn, n, piped):
+        barrier()
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2.record(cur)
+        if piped:
+            for st in (s_in, s_c, s_out):
+                st.wait_event(e2)
+            for e in ev_k + ev_o:
+                e.record(cur)
+        for i in range(n):
+            fn(i) if piped else fn()
+        if piped:
+            for st in (s_in, s_c, s_out):
+                cur.wait_stream(st)
+        e3.record(cur)
+        barrier()
+        t = torch.tensor([e2.elapsed_time(e3) / n], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    n_e2e = max(6, min(args.steps, 20))
+    timed(serial_step, 3, False)
+    serial_ms = timed(serial_step, n_e2e, False)
+    timed(piped_step, 4, True)
+    piped_ms = timed(piped_step, n_e2e, True)
+    return piped_ms, serial_ms
 
 
 def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
@@ -398,8 +447,11 @@ def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flop
                               if args.router == "gemv" else "fp32 logits supplied by the caller")},
         "clocks": clk.summary(),
         "e2e": (None if e2e_ms is None else
-                {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
-                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}),
+                {"value": flops / (e2e_ms[0] * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms[0],
+                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                 "schedule": "steps software-pipelined over three streams (upload | kernel | download), two input "
+                             "slots; every step copies its own inputs and result",
+                 "serial_ms_per_step": e2e_ms[1], "serial_value": flops / (e2e_ms[1] * 1e-3) / 1e12}),
         "gpu_launches": args.steps,
         "kernel_ms": kern_ms,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,

@@ -87,6 +87,20 @@ def test_pre_launch_return_codes(built_libs):
     # a map handed to a build without expert parallelism
     a, keep = _args(extra=[vp(0), p])
     assert lib.launch_prefill_moe_wgmma_q1_ep(*a) == -121
+    # the entry with the router linear inside: weight and logits buffer are both required, and the
+    # remaining arguments are checked like those of the other entries
+    lib.prefill_wgmma_has_router_gemv.restype = ctypes.c_int
+    assert lib.prefill_wgmma_has_router_gemv() == 1
+    tail = [vp(0), vp(0), vp(0), ci(0), ci(1), ci(1), ci(0), ctypes.c_uint(0), vp(0), vp(0), ctypes.c_float(1.0), vp(0)]
+
+    def gemv(rw, lg, **kw):
+        a, k = _args(extra=tail, **kw)
+        return lib.launch_prefill_moe_wgmma_q1_gemv(rw, lg, *a[1:])
+
+    assert gemv(vp(0), p) == -105
+    assert gemv(p, vp(0)) == -105
+    assert gemv(p, p, n_tokens=0) == -101
+    assert gemv(p, p, ws_bytes=16) == -100
 
 
 def test_expert_parallel_build_declines_without_map(built_libs):

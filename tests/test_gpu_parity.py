@@ -205,6 +205,23 @@ def test_deepseek_tp8_shard_grouped_router(gu, oracle, T):
         r2 = gu.launch(gu.kernel("ds_tp8"), gl, {"hs": hs, "logits": lg})
         rows = np.setdiff1d(np.arange(lg.shape[0]), g["tie_rows"])
         assert (np.sort(r2["ids"], 1)[rows] == g["grouped_ids_sorted_fp32"][rows]).all()
+    # the router linear inside the launch, K = 7168: logits close to an fp64 linear, routing bit-exact on the
+    # kernel's own logits, output identical to the logits-in entry fed with them
+    mk = gu.kernel("ds_tp8")
+    from unimonomoe_b200.loader import prepare_router_weight
+    rw16 = prepare_router_weight(layer["router_w"].to(torch.bfloat16))
+    out = torch.full((T, 7168), float("nan"), dtype=torch.bfloat16, device=gu.DEV)
+    sc = mk.scratch(T, gu.DEV)
+    mk.prefill_impl(batch["hs"], None, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], 8, True,
+                    layer["bias"], out, check=True, router_weight=rw16)
+    lk = sc["logits"].clone()
+    ids_k, w_k = sc["topk_ids"].cpu().numpy(), sc["topk_weights"].cpu().numpy()
+    ref64 = batch["hs"].double() @ rw16.double().t()
+    assert float((lk.double() - ref64).abs().max()) <= 1e-4
+    ids2, w2, _ = oracle.route(lk, mode=2, bias=layer["bias"])
+    assert (ids_k == ids2).all() and (w_k.view(np.uint32) == w2.view(np.uint32)).all()
+    r3 = gu.launch(mk, layer, {"hs": batch["hs"], "logits": lk}, poison=False)
+    assert torch.equal(r3["out"].view(torch.int16), out.view(torch.int16))
 
 
 def test_folded_residual_and_output_scale(gu, oracle, qwen_full):
