@@ -226,9 +226,9 @@ def main() -> None:
     spec = synth.QWEN if args.model == "qwen" else synth.DEEPSEEK
     T = args.tokens
     if args.model == "deepseek":
-        if world not in (4, 8):
-            raise SystemExit("the DeepSeek-V3 geometry is built as 1/4 and 1/8 width shards only: use --gpus 4 or 8")
-        variant, par = f"ds_tp{world}", f"tp{world}"
+        if world not in (1, 2, 4, 8):
+            raise SystemExit("the DeepSeek-V3 geometry is built for 1, 2, 4 and 8 GPUs (tensor parallel)")
+        variant, par = ("ds_w1", "none") if world == 1 else (f"ds_tp{world}", f"tp{world}")
         n = spec.inter // world
         kw = {"inter_slice": (rank * n, (rank + 1) * n), "chunk": 8}
     elif world == 1:
@@ -439,8 +439,8 @@ def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flop
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": f"{spec.name} MoE layer prefill, T={T} tokens, H=2048, E=256, top-8, I=512, "
-                               f"block-FP8 [128,128] weights", "tokens": T, "parallelism": par, "variant": variant,
+        "config": {"workload": f"{spec.name} MoE layer prefill, T={T} tokens, H={spec.hidden}, E=256, top-8, "
+                               f"I={spec.inter}, block-FP8 [128,128] weights", "tokens": T, "parallelism": par, "variant": variant,
                    "l2_policy": "inputs larger than L2: 805 MB of weights + 0.5 GB of partial rows stream per step",
                    "reduce": reduce_desc,
                    "router": ("bf16 router linear inside the launch (its 2*T*H*E FLOPs are not counted)"

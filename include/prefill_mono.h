@@ -166,6 +166,14 @@ int launch_prefill_moe_wgmma_q1_gemv(const void* router_w_bf16, float* logits_ou
                                      const int32_t* expert_map, prefill_mono_stream_t stream);
 
 int prefill_wgmma_arch(void);                 /* 100 = built for sm_100a */
+/* 1 = tiles run as pairs on clusters of two CTAs (tcgen05 cta_group::2); the total_tiles word of the
+ * workspace then counts pairs, and launch_prefill_moe_wgmma_q1_gemv returns -106 (no router linear).
+ * -107 from any launch: fewer than grid_size/2 two-CTA clusters can be resident on this device. */
+int prefill_wgmma_cta_pair(void);
+/* Chunks the intermediate is processed in: 1 up to N_HALF = 512, N_HALF/512 beyond. output_accum holds
+ * num_tokens * top_k * chunks rows of H bf16 values (the reference's fp32 [T*8, H] allocation is large
+ * enough for 1 or 2 chunks). */
+int prefill_wgmma_partial_chunks(void);
 int prefill_wgmma_block_threads(void);        /* threads per CTA */
 int prefill_wgmma_stable_sort(void);          /* 1 = sorted_token_ids is deterministic (stable) */
 /* Bounded waits: every device-side wait gives up after the time limit, records

@@ -112,10 +112,12 @@ def quant_act(act_bf16):
 
 
 def moe_path(tokens, act_q, act_scale, ids, weights, w13, w13_scale, w2, w2_scale, out_scale=1.0,
-             residual=None, want_dumps=False):
+             residual=None, want_dumps=False, chunk_cols=512):
     """Path-faithful expert computation for the listed tokens. Returns out [n_sel,H] as a
-    bf16 torch tensor, and with want_dumps also (partial bf16 [n_sel*k,H], acc fp32
-    [n_sel*k, 2*n_half], inter uint8 [n_sel*k, n_half], iscale fp32 [n_sel*k, n_half/128])."""
+    bf16 torch tensor, and with want_dumps also (partial bf16 [n_sel*k*nch,H], acc fp32
+    [n_sel*k, 2*n_half], inter uint8 [n_sel*k, n_half], iscale fp32 [n_sel*k, n_half/128]).
+    An intermediate wider than chunk_cols columns yields one bf16 partial row per chunk (nch of them),
+    as the kernel processes it."""
     tokens = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32))
     act_q = _np(act_q, np.uint8)
     act_scale = _np(act_scale, np.float32)
@@ -134,13 +136,14 @@ def moe_path(tokens, act_q, act_scale, ids, weights, w13, w13_scale, w2, w2_scal
     out = np.empty((n_sel, H), np.uint16)
     part = acc = inter = isc = None
     if want_dumps:
-        part = np.empty((n_sel * top_k, H), np.uint16)
+        nch = max(1, n_half // chunk_cols) if n_half > chunk_cols else 1
+        part = np.empty((n_sel * top_k * nch, H), np.uint16)
         acc = np.empty((n_sel * top_k, n_up), np.float32)
         inter = np.empty((n_sel * top_k, n_half), np.uint8)
         isc = np.empty((n_sel * top_k, n_half // 128), np.float32)
     lib().oracle_moe_path(_p(tokens), n_sel, top_k, K, H, n_half, n_local, _p(act_q), _p(act_scale), _p(ids),
                           _p(weights), _p(w13), _p(w13_scale), _p(w2), _p(w2_scale), ctypes.c_float(out_scale),
-                          _p(res), _p(out), _p(part), _p(acc), _p(inter), _p(isc))
+                          _p(res), _p(out), _p(part), _p(acc), _p(inter), _p(isc), int(chunk_cols))
     out_t = torch.from_numpy(out.view(np.int16)).view(torch.bfloat16)
     if want_dumps:
         return out_t, torch.from_numpy(part.view(np.int16)).view(torch.bfloat16), acc, inter, isc

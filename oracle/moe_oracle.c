@@ -313,17 +313,22 @@ void oracle_moe_path(const int32_t* tokens, int n_sel, int top_k, int K, int H, 
                      const uint8_t* act_q, const float* act_scale, const int32_t* ids, const float* weights,
                      const uint8_t* w13, const float* w13_scale, const uint8_t* w2, const float* w2_scale,
                      float out_scale, const uint16_t* residual_bf16, uint16_t* out_bf16, uint16_t* partial_bf16,
-                     float* acc_dump, uint8_t* inter_dump, float* iscale_dump) {
+                     float* acc_dump, uint8_t* inter_dump, float* iscale_dump, int chunk_cols) {
   ensure_lut();
   const int nk = K / 128, np = n_half / 128, n_up = 2 * n_half;
+  /* An intermediate wider than one chunk is processed chunk by chunk: every chunk of columns yields its
+   * own bf16 partial row (times the routing weight), and the slot sum adds slots in ascending order and,
+   * inside a slot, chunks in ascending order. partial is [n_pairs * nch, H]. */
+  const int cc = (chunk_cols > 0 && chunk_cols < n_half) ? chunk_cols : n_half;
+  const int nch = n_half / cc, npc = cc / 128;
   const int n_pairs = n_sel * top_k;
   uint16_t* partial = partial_bf16;
   int own_partial = 0;
   if (!partial) {
-    partial = (uint16_t*)calloc((size_t)n_pairs * H, sizeof(uint16_t));
+    partial = (uint16_t*)calloc((size_t)n_pairs * nch * H, sizeof(uint16_t));
     own_partial = 1;
   } else {
-    memset(partial, 0, (size_t)n_pairs * H * sizeof(uint16_t));
+    memset(partial, 0, (size_t)n_pairs * nch * H * sizeof(uint16_t));
   }
   if (acc_dump) memset(acc_dump, 0, sizeof(float) * (size_t)n_pairs * n_up);
   if (inter_dump) memset(inter_dump, 0, (size_t)n_pairs * n_half);
@@ -404,15 +409,17 @@ void oracle_moe_path(const int32_t* tokens, int n_sel, int top_k, int K, int H, 
           if (iscale_dump) iscale_dump[(size_t)pair * np + b] = isc[b];
         }
         for (int h = 0; h < H; ++h) {
-          float acc = 0.f;
           const float* wr = w2f + (size_t)h * n_half;
-          for (int dk = 0; dk < np; ++dk) {
-            const float sc = s2[(size_t)(h / 128) * np + dk] * isc[dk];
-            acc = fmaf(dot128(qf + dk * 128, wr + dk * 128), sc, acc);
+          for (int c = 0; c < nch; ++c) {
+            float acc = 0.f;
+            for (int dk = c * npc; dk < (c + 1) * npc; ++dk) {
+              const float sc = s2[(size_t)(h / 128) * np + dk] * isc[dk];
+              acc = fmaf(dot128(qf + dk * 128, wr + dk * 128), sc, acc);
+            }
+            float v = acc * rw;
+            v = fminf(fmaxf(v, -3.38953139e38f), 3.38953139e38f);
+            partial[((size_t)pair * nch + c) * H + h] = float_to_bf16(v);
           }
-          float v = acc * rw;
-          v = fminf(fmaxf(v, -3.38953139e38f), 3.38953139e38f);
-          partial[(size_t)pair * H + h] = float_to_bf16(v);
         }
       }
     }
@@ -426,7 +433,8 @@ void oracle_moe_path(const int32_t* tokens, int n_sel, int top_k, int K, int H, 
       float s = 0.f;
       for (int k = 0; k < top_k; ++k) {
         const int e = ids[(size_t)t * top_k + k];
-        if (e >= 0 && e < n_local) s += bf16_to_float(partial[(size_t)(i * top_k + k) * H + h]);
+        if (e >= 0 && e < n_local)
+          for (int c = 0; c < nch; ++c) s += bf16_to_float(partial[((size_t)(i * top_k + k) * nch + c) * H + h]);
       }
       float o;
       if (residual_bf16) o = fmaf(s, out_scale, bf16_to_float(residual_bf16[(size_t)t * H + h]));

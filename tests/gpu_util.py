@@ -38,7 +38,7 @@ def launch(mk, layer, batch, expert_map=None, poison=True):
     }
 
 
-def check_routing(O, res, batch, mode, bias, n_local, expert_map=None):
+def check_routing(O, res, batch, mode, bias, n_local, expert_map=None, rows_per_unit=128):
     """Expert ids, weights, counts, offsets and the sort permutation must be bit-exact."""
     ids, w, gids = O.route(batch["logits"], mode=mode, bias=bias, expert_map=expert_map)
     assert (res["ids"] == ids).all(), f"{int((res['ids'] != ids).any(1).sum())} tokens routed differently"
@@ -47,7 +47,9 @@ def check_routing(O, res, batch, mode, bias, n_local, expert_map=None):
     assert (res["counts"][:n_local] == cnt).all()
     assert (res["offsets"][:n_local + 1] == off).all()
     assert (res["sorted"][:len(srt)] == srt).all()
-    assert res["total_tiles"] == int(((cnt + 127) // 128).sum())
+    # scheduling units: tiles of 128 sorted rows, or pairs of them in the two-CTA build
+    if rows_per_unit is not None:   # builds that process a tile in chunks count (tile, chunk) units instead
+        assert res["total_tiles"] == int(((cnt + rows_per_unit - 1) // rows_per_unit).sum())
     return ids, w, gids
 
 

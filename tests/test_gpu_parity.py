@@ -57,6 +57,21 @@ def test_qwen_single_gpu_parity(gu, oracle, qwen_full, T):
     gu.check_output(oracle, res["out"], gu.sample_tokens(T, 48), q, s, ids, w, qwen_full)
 
 
+@pytest.mark.parametrize("T", [7, 1000, 16384])
+def test_two_cta_pair_build_matches(gu, oracle, qwen_full, T):
+    """The build that runs pairs of tiles on clusters of two CTAs (tcgen05 cta_group::2, M = 256, each
+    CTA loading half of every weight stage) passes the same bit-exact routing checks and produces the same
+    output bytes as the one-CTA build: the arithmetic per row is identical, only the schedule differs."""
+    mk2 = gu.kernel("qwen_w1_pair")
+    assert mk2._int_symbol("cta_pair") == 1
+    batch = synth.make_batch(synth.QWEN, qwen_full, T, seed=5, device=gu.DEV)
+    res2 = gu.launch(mk2, qwen_full, batch)
+    gu.check_routing(oracle, res2, batch, 0, None, 256, rows_per_unit=256)
+    assert torch.isfinite(res2["out"].float()).all()
+    res1 = gu.launch(gu.kernel("qwen_w1"), qwen_full, batch)
+    assert torch.equal(res1["out"].view(torch.int16), res2["out"].view(torch.int16))
+
+
 def test_run_to_run_bitwise_and_token_permutation(gu, oracle, qwen_full):
     """Full-size property checks: two launches agree bit for bit, and permuting the tokens
     permutes the output rows bit for bit (a row's arithmetic does not depend on its tile)."""
@@ -222,6 +237,26 @@ def test_deepseek_tp8_shard_grouped_router(gu, oracle, T):
     assert (ids_k == ids2).all() and (w_k.view(np.uint32) == w2.view(np.uint32)).all()
     r3 = gu.launch(mk, layer, {"hs": batch["hs"], "logits": lk}, poison=False)
     assert torch.equal(r3["out"].view(torch.int16), out.view(torch.int16))
+
+
+@pytest.mark.parametrize("variant,width", [("ds_tp2", 1024), ("ds_w1", 2048)])
+def test_deepseek_wide_shards_run_in_chunks(gu, oracle, variant, width):
+    """DeepSeek-V3 geometry at 1/2 and full expert width: the intermediate (1024 / 2048 columns) exceeds
+    what shared memory holds as one e4m3 tile, so every tile is processed in chunks of 512 columns, each
+    chunk leaving its own bf16 partial row. Routing stays bit-exact; the output meets the same bounds
+    against the oracle, which rounds per chunk in the same way."""
+    mk = gu.kernel(variant)
+    assert mk._int_symbol("partial_chunks") == width // 512
+    layer = synth.make_layer(synth.DEEPSEEK, seed=0, device=gu.DEV, inter_slice=(0, width), with_shared=False, chunk=8)
+    for T in (96, 1000):
+        batch = synth.make_batch(synth.DEEPSEEK, layer, T, seed=1, device=gu.DEV)
+        res = gu.launch(mk, layer, batch)
+        ids, w, _ = gu.check_routing(oracle, res, batch, 2, layer["bias"], 256, rows_per_unit=None)
+        q, s = gu.check_act_quant(oracle, res, batch)
+        assert torch.isfinite(res["out"].float()).all()
+        gu.check_output(oracle, res["out"], gu.sample_tokens(T, 6), q, s, ids, w, layer)
+    del layer
+    torch.cuda.empty_cache()
 
 
 def test_folded_residual_and_output_scale(gu, oracle, qwen_full):

@@ -32,6 +32,11 @@ VARIANTS = {
     "qwen_ep8": dict(QWEN, N_HALF=512, E_LOCAL=32),
     "ds_tp8": dict(DS, N_HALF=256, E_LOCAL=256),      # DeepSeek-V3-like, 1/8 width shard
     "ds_tp4": dict(DS, N_HALF=512, E_LOCAL=256),
+    "ds_tp2": dict(DS, N_HALF=1024, E_LOCAL=256),     # intermediate processed in 2 chunks of 512 columns
+    "ds_w1": dict(DS, N_HALF=2048, E_LOCAL=256),      # full width on one GPU: 4 chunks
+    # tiles scheduled as pairs on clusters of two CTAs (tcgen05 cta_group::2); measured equal in speed to
+    # qwen_w1 at 16384 tokens (fewer L2 weight bytes per SM, but 11 % more padded rows), so not the default
+    "qwen_w1_pair": dict(QWEN, N_HALF=512, E_LOCAL=256, PAIR=1),
 }
 
 # development variants (not built by default): other epilogue shapes, and the stall-counter build
@@ -39,10 +44,12 @@ DEV_VARIANTS = {
     "qwen_w1_n2": dict(QWEN, N_HALF=512, E_LOCAL=256, EPI_WGS=2, NSPLIT=2),
     "qwen_w1_prof": dict(QWEN, N_HALF=512, E_LOCAL=256, PROFILE=1),
     "qwen_w1_plainst": dict(QWEN, N_HALF=512, E_LOCAL=256, PLAIN_STORES=1),
+    "qwen_w1_pair_prof": dict(QWEN, N_HALF=512, E_LOCAL=256, PAIR=1, PROFILE=1),
+    **{f"qwen_w1_pair_abl{m}": dict(QWEN, N_HALF=512, E_LOCAL=256, PAIR=1, ABLATE=m) for m in (1, 4, 6, 7)},
     **{f"qwen_w1_abl{m}": dict(QWEN, N_HALF=512, E_LOCAL=256, NSPLIT=1, ABLATE=m) for m in (1, 4, 7, 15, 23, 31)},
 }
 
-SOURCES = ["mono_kernel.cu", "ptx_sm100.cuh", "bounded_wait.cuh", "route_math.cuh"]
+SOURCES = ["mono_kernel.cu", "ptx_sm100.cuh", "pair_sm100.cuh", "bounded_wait.cuh", "route_math.cuh"]
 
 
 def lib_path(variant: str) -> str:
@@ -68,7 +75,7 @@ def build_variant(variant: str, force: bool = False, verbose: bool = False) -> s
         "-Xptxas", "-v", "-shared", "-Xcompiler", "-fPIC",
         f"-DMONO_K_DIM={g['K']}", f"-DMONO_H_DIM={g['H']}", f"-DMONO_N_HALF={g['N_HALF']}",
         f"-DMONO_E_LOCAL={g['E_LOCAL']}", f"-DMONO_ROUTER_MODE={g['MODE']}", f"-DMONO_EPI_WGS={g.get('EPI_WGS', 2)}", f"-DMONO_NSPLIT={g.get('NSPLIT', 1)}",
-        *(["-DMONO_PROFILE"] if g.get("PROFILE") else []), *(["-DMONO_PLAIN_STORES"] if g.get("PLAIN_STORES") else []), f"-DMONO_ABLATE={g.get('ABLATE', 0)}",
+        *(["-DMONO_PROFILE"] if g.get("PROFILE") else []), *(["-DMONO_PLAIN_STORES"] if g.get("PLAIN_STORES") else []), f"-DMONO_ABLATE={g.get('ABLATE', 0)}", f"-DMONO_PAIR={g.get('PAIR', 0)}",
         os.path.join(CSRC, "mono_kernel.cu"), "-o", out,
     ]
     r = subprocess.run(cmd, capture_output=True, text=True)

@@ -38,6 +38,7 @@
 #include <cstdlib>
 
 #include "bounded_wait.cuh"
+#include "pair_sm100.cuh"
 #include "ptx_sm100.cuh"
 #include "route_math.cuh"
 
@@ -93,7 +94,15 @@ constexpr int ROUTER_MODE = MONO_ROUTER_MODE;
 constexpr int N_GROUP = 8;
 constexpr int TOPK_GROUP = 4;
 constexpr int NK = K_DIM / 128;    // K slabs of the up projection
-constexpr int NP = N_HALF / 128;   // 128-column passes of the up projection = K slabs of the down projection
+// An intermediate wider than 512 columns does not fit in shared memory as one e4m3 tile, so a tile is
+// then processed in NCH chunks of 512 intermediate columns. Each (tile, chunk) is an independent unit of
+// work: up projection of the chunk's gate/up columns, SiLU, requantisation, and the down projection over
+// the chunk's K range, which yields its own bf16 partial row; the slot sum adds top_k * NCH rows per token.
+constexpr int NPT = N_HALF / 128;  // 128-column blocks of the whole intermediate
+constexpr int CHUNK_COLS = N_HALF > 512 ? 512 : N_HALF;
+constexpr int NCH = N_HALF / CHUNK_COLS;
+constexpr int NP = CHUNK_COLS / 128;  // 128-column passes of the up projection = K slabs of the down projection, per chunk
+static_assert(N_HALF % CHUNK_COLS == 0, "the intermediate splits into whole chunks");
 constexpr int NHB = H_DIM / 256;   // 256-column passes of the down projection
 constexpr int TILE_M = 128;
 
@@ -116,8 +125,17 @@ static_assert(ROUTER_MODE != 2 || N_GROUP * 32 == E, "grouped routing assumes 32
 #ifndef MONO_NSPLIT
 #define MONO_NSPLIT 1
 #endif
+// MONO_PAIR=1: tiles are scheduled as pairs of 128-row tiles of one expert on a cluster of two CTAs
+// (tcgen05 cta_group::2, M = 256). Each CTA gathers its own 128 activation rows and loads HALF of every
+// weight stage; one thread of the cluster's rank-0 CTA issues the MMAs for both. Halves the weight
+// bytes every SM pulls from L2 and makes room for deeper operand rings.
+#ifndef MONO_PAIR
+#define MONO_PAIR 0
+#endif
+constexpr bool PAIR = MONO_PAIR != 0;
 constexpr int EPI_WGS = MONO_EPI_WGS;
 static_assert(EPI_WGS == 2 || EPI_WGS == 4, "two or four epilogue warpgroups");
+static_assert(!PAIR || (EPI_WGS == 2 && MONO_NSPLIT == 1), "the pair schedule is written for two epilogue warpgroups, N = 256");
 // A 128-deep K slab of the 256 weight rows of a stage is issued as NSPLIT independent MMAs of
 // N = BC columns, each into its own TMEM buffer, so the epilogue's read-out of one buffer is a
 // single short dependency chain and the MMA thread can run NBUF-1 buffers ahead of it.
@@ -137,12 +155,14 @@ constexpr int BLOCK = 128 + N_EPI;
 constexpr int NWARPS = BLOCK / 32;
 constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_GATHER0 = 2;  // warps 2,3 gather; warps 4.. epilogue
 constexpr int N_GATHER = 64;
-constexpr int MAX_MY_TILES = 32;
+constexpr int MAX_MY_TILES = 32 * NCH;
 constexpr int MAX_TILES = MAX_MY_TILES * kGrid;
 
 // ------------------------------------------------------------------ shared memory plan
 constexpr int A_STAGE_BYTES = TILE_M * 128;  // 128 rows x 128 B
-constexpr int B_STAGE_BYTES = 256 * 128;     // 256 weight rows x 128 B
+constexpr int B_ROWS = PAIR ? 128 : 256;     // weight rows of a stage kept by one CTA
+constexpr int B_STAGE_BYTES = B_ROWS * 128;  // x 128 B
+constexpr int STAGE_CAP = PAIR ? 6 : 4;
 constexpr int INTER_BYTES = NP * A_STAGE_BYTES;
 constexpr int SMEM_CAP = 227 * 1024;
 constexpr int SMEM_STATIC_RESERVE = 6 * 1024;
@@ -156,9 +176,9 @@ static_assert(NK % 8 == 0, "each epilogue thread stages NK/2 activation scales i
 static_assert(NHB >= AS_PIECES + 2, "the next tile's scales are staged during the down projection");
 constexpr int SMEM_AVAIL = SMEM_CAP - SMEM_STATIC_RESERVE - 1024 - INTER_BYTES - SCALE_BYTES;
 constexpr int SB_RAW = SMEM_AVAIL / (A_STAGE_BYTES + B_STAGE_BYTES);
-constexpr int SB = SB_RAW > 4 ? 4 : SB_RAW;
+constexpr int SB = SB_RAW > STAGE_CAP ? STAGE_CAP : SB_RAW;
 constexpr int SA_RAW = (SMEM_AVAIL - SB * B_STAGE_BYTES) / A_STAGE_BYTES;
-constexpr int SA = SA_RAW > 4 ? 4 : SA_RAW;
+constexpr int SA = SA_RAW > STAGE_CAP ? STAGE_CAP : SA_RAW;
 static_assert(SB >= 2 && SA >= 2, "intermediate too wide for shared memory: shard N_HALF further");
 constexpr int DYN_SMEM = 1024 + INTER_BYTES + SA * A_STAGE_BYTES + SB * B_STAGE_BYTES + SCALE_BYTES;
 static_assert(NWARPS * E * 4 <= SA * A_STAGE_BYTES, "phase-0 histograms live in the activation ring");
@@ -175,7 +195,7 @@ static_assert(128 * REGS_PRODUCER + N_EPI * REGS_EPILOGUE <= BLOCK * REGS_LAUNCH
 static_assert(REGS_LAUNCH * BLOCK <= 65536, "launch register count exceeds the register file");
 
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t IDESC = umma_idesc_e4m3_f32(128, BC);
+constexpr uint32_t IDESC = umma_idesc_e4m3_f32(PAIR ? 256 : 128, BC);
 // router GEMV: one [128 tokens x 256 experts] accumulator, K slabs of 64 bf16 (128 bytes)
 constexpr uint32_t IDESC_ROUTER = umma_idesc_bf16_f32(128, E);
 constexpr int RK = K_DIM / 64;
@@ -225,7 +245,7 @@ struct Params {
 };
 
 struct TileInfo {
-  int e, row0, rows, pad;
+  int e, row0, rows, chunk;
 };
 
 // ------------------------------------------------------------------ small helpers
@@ -420,9 +440,20 @@ __device__ __forceinline__ void quantize_activations(const Params& p, int gwarp,
   }
 }
 
+// Position, in the expert's scale tensors, of entry i of the per-chunk staging arrays:
+// up scales [2 * NPT, NK] -> staged [gate NP rows | up NP rows] x NK; down scales [H/128, NPT] -> staged [H/128, NP].
+__device__ __forceinline__ size_t wsu_index(int e, int chunk, int i) {
+  const int half = i / (NP * NK), rem = i % (NP * NK);
+  return static_cast<size_t>(e) * (2 * NPT * NK) + static_cast<size_t>(half * NPT + chunk * NP) * NK + rem;
+}
+__device__ __forceinline__ size_t wsd_index(int e, int chunk, int i) {
+  const int hb = i / NP, dk = i % NP;
+  return static_cast<size_t>(e) * ((H_DIM / 128) * NPT) + static_cast<size_t>(hb) * NPT + chunk * NP + dk;
+}
+
 // ------------------------------------------------------------------ shared state
 struct __align__(16) SharedState {
-  uint64_t fullA[4], emptyA[4], fullB[4], emptyB[4];
+  uint64_t fullA[STAGE_CAP], emptyA[STAGE_CAP], fullB[STAGE_CAP], emptyB[STAGE_CAP];
   uint64_t tmem_full[NBUF], tmem_empty[NBUF];
   uint64_t inter_ready;
   uint64_t rfull[4], rempty[4], racc_full, racc_empty;  // phase R only
@@ -486,7 +517,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
   // core's fp32 accumulator over K slabs of 64 in ascending order (its order inside one instruction is
   // the hardware's). One accumulator of 128 tokens x 256 experts in tensor memory; TMA brings one
   // [128 x 64] slab of x and one [256 x 64] slab of W_r per stage, both in the 128-byte swizzle.
-  const bool gemv = p.logits_out != nullptr;
+  const bool gemv = !PAIR && p.logits_out != nullptr;  // the pair build keeps every tcgen05 instruction at cta_group::2
   if (gemv) {
     if (tid == 0) {
       for (int s = 0; s < RS; ++s) { mbar_init(&S.rfull[s], 1); mbar_init(&S.rempty[s], 1); }
@@ -628,6 +659,10 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
   if (bid == 0 && tid == 0) ws->phase_ns[1] = globaltimer_ns();
 
   // ================================================================ phase 1
+  // Scheduling unit: a tile of 128 sorted rows on one CTA, or a pair of them on a cluster of two CTAs.
+  constexpr int SCHED_ROWS = PAIR ? 2 * TILE_M : TILE_M;
+  constexpr int SCHED_UNITS = PAIR ? kGrid / 2 : kGrid;
+  const int sched_me = PAIR ? (bid >> 1) : bid;
   if (alive) {
     if (tid < E) { ph1_tot[tid] = 0; ph1_pre[tid] = 0; }
     __syncthreads();
@@ -650,7 +685,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
     int cnt = 0, tiles_e = 0;
     if (tid < E) {
       cnt = ph1_tot[tid];
-      tiles_e = (cnt + TILE_M - 1) / TILE_M;
+      tiles_e = (cnt + SCHED_ROWS - 1) / SCHED_ROWS * NCH;  // units of work: (tile, chunk), chunk fastest
       scan_cnt[tid] = cnt;
       scan_tile[tid] = tiles_e;
     }
@@ -676,14 +711,15 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       }
       for (int i = 0; i < tiles_e; ++i) {
         const int g = tbase + i;
-        if (g % kGrid == bid) {
-          const int slot = g / kGrid;
+        if (g % SCHED_UNITS == sched_me) {
+          const int slot = g / SCHED_UNITS;
           if (slot < MAX_MY_TILES) {
             TileInfo ti;
             ti.e = tid;
-            ti.row0 = off_e + i * TILE_M;
-            ti.rows = min(TILE_M, off_e + cnt - ti.row0);
-            ti.pad = 0;
+            // pair schedule: rank 0 of the cluster takes the first 128 rows of the 256, rank 1 the rest (maybe none)
+            ti.row0 = off_e + (i / NCH) * SCHED_ROWS + (PAIR ? (bid & 1) * TILE_M : 0);
+            ti.rows = max(0, min(TILE_M, off_e + cnt - ti.row0));
+            ti.chunk = i % NCH;
             S.tiles[slot] = ti;
           } else {
             report_error(ws, kErrBounds, 1, static_cast<uint32_t>(g), static_cast<uint32_t>(slot));
@@ -702,7 +738,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
     __syncthreads();
     if (tid == 0) {
       const int tt = S.total_tiles;
-      S.n_my_tiles = (tt > bid) ? min(MAX_MY_TILES, (tt - bid + kGrid - 1) / kGrid) : 0;
+      S.n_my_tiles = (tt > sched_me) ? min(MAX_MY_TILES, (tt - sched_me + SCHED_UNITS - 1) / SCHED_UNITS) : 0;
     }
     // stable scatter: each warp re-walks its own tokens in ascending order
     for (int t = t_begin; t < t_end; ++t) {
@@ -722,20 +758,39 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
   if (bid == 0 && tid == 0) ws->phase_ns[2] = globaltimer_ns();
 
   // ================================================================ phase 2
+  // Pair build: the MMA thread lives in the cluster's rank-0 CTA ("leader"). Its fullA barrier also
+  // receives one forwarded arrival per stage for the peer's gathered rows, and its tmem_empty /
+  // inter_ready barriers collect the epilogue warps of both CTAs.
+  const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = crank == 0u;
   if (tid == 0) {
-    for (int s = 0; s < SA; ++s) { mbar_init(&S.fullA[s], N_GATHER); mbar_init(&S.emptyA[s], 1); }
+    const uint32_t both = PAIR ? 2u : 1u;
+    for (int s = 0; s < SA; ++s) {
+      mbar_init(&S.fullA[s], N_GATHER + ((PAIR && leader) ? 1u : 0u));
+      mbar_init(&S.emptyA[s], 1);
+    }
     for (int s = 0; s < SB; ++s) { mbar_init(&S.fullB[s], 1); mbar_init(&S.emptyB[s], 1); }
-    for (int s = 0; s < NBUF; ++s) { mbar_init(&S.tmem_full[s], 1); mbar_init(&S.tmem_empty[s], N_EPI / 32); }
-    mbar_init(&S.inter_ready, N_EPI / 32);
+    for (int s = 0; s < NBUF; ++s) { mbar_init(&S.tmem_full[s], 1); mbar_init(&S.tmem_empty[s], both * (N_EPI / 32)); }
+    mbar_init(&S.inter_ready, both * (N_EPI / 32));
     mbar_init_fence();
   }
   if (warp == WARP_MMA && !gemv) {  // phase R already holds the allocation
-    tmem_alloc(&S.tmem_base, TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(&S.tmem_base, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&S.tmem_base, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  else __syncthreads();
   tc_fence_after();
+  // cluster address of the leader's copy of a barrier of the shared state (both CTAs signal it)
+  const uint32_t s_local = smem_u32(&S);
+  const uint32_t s_leader = PAIR ? map_to_cta(s_local, 0) : s_local;
+  auto at_leader = [&](const uint64_t* bar) -> uint32_t { return s_leader + (smem_u32(bar) - s_local); };
   const uint32_t tmem_base = S.tmem_base;
   const int n_my = alive ? S.n_my_tiles : 0;
 
@@ -750,19 +805,30 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         bool ok = true;
         PROF_DECL(pw_emptyB);
         for (int it = 0; it < n_my && ok; ++it) {
-          const int e = S.tiles[it].e;
+          const int e = S.tiles[it].e, ch = S.tiles[it].chunk;
           for (int ps = 0; ps < NP && ok; ++ps) {
-            const uint32_t yg = static_cast<uint32_t>(e * N_UP + ps * 128);
+            const uint32_t yg = static_cast<uint32_t>(e * N_UP + ch * CHUNK_COLS + ps * 128);
             const uint32_t yu = yg + N_HALF;
             for (int ks = 0; ks < NK; ++ks) {
               const uint32_t st = nb % SB, ph = (nb / SB) & 1u;
               { PROF_T0();
               if (!mbar_wait(&S.emptyB[st], ph ^ 1u, wc, kSiteEmptyB)) { ok = false; break; }
               PROF_ADD(pw_emptyB); }
-              mbar_arrive_expect_tx(&S.fullB[st], (MONO_ABLATE & 16) ? 0 : B_STAGE_BYTES);
-              if constexpr ((MONO_ABLATE & 16) != 0) { ++nb; continue; }
               uint8_t* dst = b_ring + st * B_STAGE_BYTES;
               const uint32_t x = static_cast<uint32_t>(ks * 128);
+              if constexpr (PAIR) {
+                // this CTA's half of the stage: the rows the non-pair layout gives to warpgroup `crank`
+                // (HCB gate columns, then the HCB matching up columns); the bytes of both halves are
+                // counted on the leader's barrier
+                if (leader) mbar_arrive_expect_tx(&S.fullB[st], 2 * B_STAGE_BYTES);
+                const uint32_t co = crank * HCB;
+                tma_load_2d_pair(&p.tm_up, x, yg + co, dst, at_leader(&S.fullB[st]));
+                tma_load_2d_pair(&p.tm_up, x, yu + co, dst + HCB * 128, at_leader(&S.fullB[st]));
+                ++nb;
+                continue;
+              }
+              mbar_arrive_expect_tx(&S.fullB[st], (MONO_ABLATE & 16) ? 0 : B_STAGE_BYTES);
+              if constexpr ((MONO_ABLATE & 16) != 0) { ++nb; continue; }
               // shared rows of buffer j, warpgroup h: [j*BC + h*WC, +HCB) gate columns c + j*PASS_STRIDE + h*HCB ..,
               // then the HCB matching up columns
 #pragma unroll
@@ -782,10 +848,18 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             for (int dk = 0; dk < NP; ++dk) {
               const uint32_t st = nb % SB, ph = (nb / SB) & 1u;
               if (!mbar_wait(&S.emptyB[st], ph ^ 1u, wc, kSiteEmptyB)) { ok = false; break; }
+              uint8_t* dst = b_ring + st * B_STAGE_BYTES;
+              const uint32_t x = static_cast<uint32_t>((ch * NP + dk) * 128);
+              if constexpr (PAIR) {
+                if (leader) mbar_arrive_expect_tx(&S.fullB[st], 2 * B_STAGE_BYTES);
+#pragma unroll
+                for (int j = 0; j < B_ROWS / HCB; ++j)
+                  tma_load_2d_pair(&p.tm_down, x, y + crank * B_ROWS + j * HCB, dst + j * HCB * 128, at_leader(&S.fullB[st]));
+                ++nb;
+                continue;
+              }
               mbar_arrive_expect_tx(&S.fullB[st], (MONO_ABLATE & 16) ? 0 : B_STAGE_BYTES);
               if constexpr ((MONO_ABLATE & 16) != 0) { ++nb; continue; }
-              uint8_t* dst = b_ring + st * B_STAGE_BYTES;
-              const uint32_t x = static_cast<uint32_t>(dk * 128);
 #pragma unroll
               for (int j = 0; j < 256 / HCB; ++j) tma_load_2d(&p.tm_down, x, y + j * HCB, dst + j * HCB * 128, &S.fullB[st]);
               ++nb;
@@ -796,7 +870,22 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       }
     } else if (warp == WARP_MMA) {
       // ---------------------------------------------------------- MMA issuer
-      if (lane == 0) {
+      if (PAIR && !leader) {
+        // The peer CTA issues no MMA. Its lane 0 forwards "my gathered rows of this stage have landed"
+        // to the leader's barrier (cp.async can only signal a barrier of its own CTA).
+        if (lane == 0) {
+          uint32_t na = 0;
+          bool ok = true;
+          for (int it = 0; it < n_my && ok; ++it) {
+            for (int s = 0; s < NP * NK; ++s, ++na) {
+              const uint32_t sa = na % SA;
+              if (!mbar_wait(&S.fullA[sa], (na / SA) & 1u, wc, kSiteFullA)) { ok = false; break; }
+              fence_proxy_async_smem();
+              mbar_arrive_cluster(at_leader(&S.fullA[sa]));
+            }
+          }
+        }
+      } else if (lane == 0) {
         uint32_t nb = 0, na = 0, nt = 0;
         bool ok = true;
         PROF_DECL(pm_fullB); PROF_DECL(pm_fullA); PROF_DECL(pm_tmem); PROF_DECL(pm_inter); PROF_DECL(pm_total);
@@ -823,14 +912,20 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               tc_fence_after();
               const uint64_t db = umma_desc_sw128(b_ring_u32 + sb * B_STAGE_BYTES + j * BC * 128);
               const uint32_t d = tmem_base + buf * BC;
+              if constexpr (PAIR) {
 #pragma unroll
-              for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
-              umma_commit(&S.tmem_full[buf]);
+                for (int k = 0; k < 4; ++k) umma_f8_pair(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+                umma_commit_pair(&S.tmem_full[buf]);
+              } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+                umma_commit(&S.tmem_full[buf]);
+              }
               ++nt;
             }
             if (!ok) break;
-            umma_commit(&S.emptyA[sa]);
-            umma_commit(&S.emptyB[sb]);
+            if constexpr (PAIR) { umma_commit_pair(&S.emptyA[sa]); umma_commit_pair(&S.emptyB[sb]); }
+            else { umma_commit(&S.emptyA[sa]); umma_commit(&S.emptyB[sb]); }
             ++nb; ++na;
           }
           if (!ok) break;
@@ -854,13 +949,19 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               tc_fence_after();
               const uint64_t db = umma_desc_sw128(b_ring_u32 + sb * B_STAGE_BYTES + j * BC * 128);
               const uint32_t d = tmem_base + buf * BC;
+              if constexpr (PAIR) {
 #pragma unroll
-              for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
-              umma_commit(&S.tmem_full[buf]);
+                for (int k = 0; k < 4; ++k) umma_f8_pair(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+                umma_commit_pair(&S.tmem_full[buf]);
+              } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+                umma_commit(&S.tmem_full[buf]);
+              }
               ++nt;
             }
             if (!ok) break;
-            umma_commit(&S.emptyB[sb]);
+            if constexpr (PAIR) umma_commit_pair(&S.emptyB[sb]); else umma_commit(&S.emptyB[sb]);
             ++nb;
           }
         }
@@ -943,7 +1044,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         if constexpr ((MONO_ABLATE & 1) != 0) {
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&S.tmem_empty[buf]);
+          if (lane == 0) { if (PAIR && !leader) mbar_arrive_cluster(at_leader(&S.tmem_empty[buf])); else mbar_arrive(&S.tmem_empty[buf]); }
           return;
         }
 #pragma unroll
@@ -955,7 +1056,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             // one arrival per warp: per-thread arrivals on one shared-memory word serialise
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&S.tmem_empty[buf]);
+            if (lane == 0) { if (PAIR && !leader) mbar_arrive_cluster(at_leader(&S.tmem_empty[buf])); else mbar_arrive(&S.tmem_empty[buf]); }
           }
 #pragma unroll
           for (int i = 0; i < LDW / 2; ++i) {
@@ -981,8 +1082,8 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
           nfi = __ldcg(&p.sorted_ids[tn.row0 + r]);
           if (nfi < 0 || nfi >= numel) nfi = -1;
         }
-        if (et < WSU_N) wsu_v = __ldg(p.up_w_scales + static_cast<size_t>(tn.e) * WSU_N + et);
-        if (et < WSD_N) wsd_v = __ldg(p.down_w_scales + static_cast<size_t>(tn.e) * WSD_N + et);
+        if (et < WSU_N) wsu_v = __ldg(p.up_w_scales + wsu_index(tn.e, tn.chunk, et));
+        if (et < WSD_N) wsd_v = __ldg(p.down_w_scales + wsd_index(tn.e, tn.chunk, et));
       };
       auto stage_weight_store = [&](int nx) {
         nrw = (nfi >= 0) ? __ldcg(&p.topk_weights[nfi]) : 0.f;
@@ -990,11 +1091,11 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         if (et < WSD_N) wsd_sm[(nx & 1) * WSD_N + et] = wsd_v;
         if constexpr (WSU_N > N_EPI) {
           for (int i = et + N_EPI; i < WSU_N; i += N_EPI)
-            wsu_sm[(nx & 1) * WSU_N + i] = __ldg(p.up_w_scales + static_cast<size_t>(S.tiles[nx].e) * WSU_N + i);
+            wsu_sm[(nx & 1) * WSU_N + i] = __ldg(p.up_w_scales + wsu_index(S.tiles[nx].e, S.tiles[nx].chunk, i));
         }
         if constexpr (WSD_N > N_EPI) {
           for (int i = et + N_EPI; i < WSD_N; i += N_EPI)
-            wsd_sm[(nx & 1) * WSD_N + i] = __ldg(p.down_w_scales + static_cast<size_t>(S.tiles[nx].e) * WSD_N + i);
+            wsd_sm[(nx & 1) * WSD_N + i] = __ldg(p.down_w_scales + wsd_index(S.tiles[nx].e, S.tiles[nx].chunk, i));
         }
       };
       auto as_piece_load = [&](int j) {
@@ -1053,7 +1154,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             float* d = p.dbg_acc + static_cast<size_t>(ti.row0 + r) * N_UP;
 #pragma unroll
             for (int j = 0; j < NSPLIT; ++j) {
-              const int col0 = ps * 128 + j * PASS_STRIDE + h * HCB;
+              const int col0 = ti.chunk * CHUNK_COLS + ps * 128 + j * PASS_STRIDE + h * HCB;
 #pragma unroll
               for (int i = 0; i < HCB / 2; ++i) {
                 d[col0 + 2 * i] = acc[j * (WC / 2) + i].x;
@@ -1101,17 +1202,17 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               const int col0 = j * PASS_STRIDE + h * HCB + c * 16;  // column inside the pass's 128
               *reinterpret_cast<uint4*>(irow + sw128(r, col0 / 16)) = qv;
               if (p.dbg_inter != nullptr && fi >= 0 && !dead)
-                *reinterpret_cast<uint4*>(p.dbg_inter + static_cast<size_t>(ti.row0 + r) * N_HALF + ps * 128 + col0) = qv;
+                *reinterpret_cast<uint4*>(p.dbg_inter + static_cast<size_t>(ti.row0 + r) * N_HALF + ti.chunk * CHUNK_COLS + ps * 128 + col0) = qv;
             }
           }
           if (p.dbg_inter_scale != nullptr && fi >= 0 && h == 0 && !dead)
-            p.dbg_inter_scale[static_cast<size_t>(ti.row0 + r) * NP + ps] = my_scale;
+            p.dbg_inter_scale[static_cast<size_t>(ti.row0 + r) * NPT + ti.chunk * NP + ps] = my_scale;
           PROF_ADD(pe_silu);
         }
         // publish the intermediate to the tensor core (async proxy) and release the MMA thread
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&S.inter_ready);
+        if (lane == 0) { if (PAIR && !leader) mbar_arrive_cluster(at_leader(&S.inter_ready)); else mbar_arrive(&S.inter_ready); }
 
         // ---------------- down projection, routing weight, bf16 partial rows.
         // Every epilogue thread is past the last pass's barrier, so nobody reads this tile's
@@ -1144,7 +1245,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
           if (fi >= 0 && !dead && (MONO_ABLATE & 4) == 0) {
 #pragma unroll
             for (int j = 0; j < NSPLIT; ++j) {
-              __nv_bfloat16* dst = p.partial + static_cast<size_t>(fi) * H_DIM + hb * 256 + j * BC + h * WC;
+              __nv_bfloat16* dst = p.partial + (static_cast<size_t>(fi) * NCH + ti.chunk) * H_DIM + hb * 256 + j * BC + h * WC;
 #pragma unroll
               for (int c = 0; c < WC / 16; ++c) {  // 16 bf16 = 32 bytes per store: whole sectors
                 uint32_t w[8];
@@ -1177,7 +1278,8 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
   // teardown of phase 2: when aborting, give in-flight bulk copies and MMAs time to land
   if (aborted(ws)) __nanosleep(200000);
   tc_fence_before();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // nothing of the peer is still signalling this CTA, or reading its tensor memory
+  else __syncthreads();
   // Registers go back to the launch split only now, behind the barrier. If the producer warps asked
   // for theirs back right after their own loops (a CTA without tiles reaches that point at once), they
   // could take back what they had just released before the epilogue warps were served, and the
@@ -1185,7 +1287,8 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
   if (warp < 4) reg_inc<REGS_LAUNCH>(); else reg_dec<REGS_LAUNCH>();
   if (warp == WARP_MMA) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 
   alive = grid_sync(wc, 2, &S.flag) && alive;
@@ -1221,17 +1324,18 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
           float s[W];
 #pragma unroll
           for (int i = 0; i < W; ++i) s[i] = 0.f;
-          uint4 raw[TOP_K];
+          // partial rows of the token: slot-major, chunk-minor, summed in that order
+          uint4 raw[TOP_K * NCH];
 #pragma unroll
-          for (int k = 0; k < TOP_K; ++k) {
+          for (int k = 0; k < TOP_K * NCH; ++k) {
             bool mine = true;
-            if constexpr (EP_BUILD) mine = own[k] >= 0;
+            if constexpr (EP_BUILD) mine = own[k / NCH] >= 0;
             raw[k] = make_uint4(0u, 0u, 0u, 0u);
             if (mine)
-              raw[k] = __ldcg(reinterpret_cast<const uint4*>(p.partial + (tok * TOP_K + k) * H_DIM + hv * W));
+              raw[k] = __ldcg(reinterpret_cast<const uint4*>(p.partial + (tok * (TOP_K * NCH) + k) * H_DIM + hv * W));
           }
 #pragma unroll
-          for (int k = 0; k < TOP_K; ++k) {
+          for (int k = 0; k < TOP_K * NCH; ++k) {
             const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&raw[k]);
 #pragma unroll
             for (int i = 0; i < W; ++i) s[i] += __bfloat162float(b[i]);
@@ -1424,6 +1528,12 @@ int prefill_wgmma_shm_total() { return DYN_SMEM + static_cast<int>(sizeof(Shared
 
 // ---- additions of this build (new capability = new symbol)
 int prefill_wgmma_arch() { return 100; }
+// 1: tiles run as pairs on clusters of two CTAs; the total_tiles word of the workspace then counts pairs
+int prefill_wgmma_cta_pair() { return PAIR ? 1 : 0; }
+// Chunks the intermediate is processed in (1 unless wider than 512 columns). output_accum must hold
+// num_tokens * top_k * chunks rows of H bf16 values: with 1 or 2 chunks the reference's fp32 [T*8, H]
+// allocation is large enough, beyond that the caller sizes it from this accessor.
+int prefill_wgmma_partial_chunks() { return NCH; }
 int prefill_wgmma_block_threads() { return BLOCK; }
 int prefill_wgmma_stable_sort() { return 1; }
 // Byte offset of the 32-bit status word inside the workspace and the bytes that follow it
@@ -1459,13 +1569,14 @@ static int launch_common(const void* router_w, float* logits_buf, const float* l
                                     void* tp_seqctr, const void* tp_residual, float out_scale,
                                     const int32_t* expert_map, cudaStream_t stream) {
   (void)block_m;  // the tile height is the compiled TILE_M
+  if (router_w != nullptr && PAIR) return -106;  // the pair build has no router linear
   if (router_w != nullptr) logits = logits_buf;
   if (EP_BUILD && expert_map == nullptr) return -120;
   if (!EP_BUILD && expert_map != nullptr) return -121;
   if (workspace == nullptr || workspace_bytes < sizeof(Workspace)) return -100;
   if (num_tokens <= 0) return -101;
   const long long numel = static_cast<long long>(num_tokens) * TOP_K;
-  if (numel / TILE_M + E_LOCAL > MAX_TILES) return -102;
+  if ((numel / TILE_M + E_LOCAL) * NCH > MAX_TILES) return -102;
   if (logits == nullptr || act_bf16 == nullptr || act_fp8 == nullptr || act_scales == nullptr ||
       up_w_fp8 == nullptr || up_w_scales == nullptr || down_w_fp8 == nullptr || down_w_scales == nullptr ||
       output_accum == nullptr || topk_ids == nullptr || topk_weights == nullptr || sorted_token_ids == nullptr ||
@@ -1543,6 +1654,37 @@ static int launch_common(const void* router_w, float* logits_buf, const float* l
   err = cudaMemsetAsync(workspace, 0, sizeof(Workspace), stream);
   if (err != cudaSuccess) return static_cast<int>(err);
 
+  if constexpr (PAIR) {
+    // 74 clusters of two CTAs; both CTAs of a cluster run on the two SMs of one TPC
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kGrid);
+    cfg.blockDim = dim3(BLOCK);
+    cfg.dynamicSmemBytes = DYN_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    static int clusters_fit = -1;   // every cluster has to be resident at once (grid barriers)
+    if (clusters_fit < 0) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, moe_prefill_kernel, &cfg) != cudaSuccess) n = 0;
+      clusters_fit = n;
+    }
+    if (clusters_fit < kGrid / 2) {
+      fprintf(stderr, "only %d of %d two-CTA clusters can be resident\n", clusters_fit, kGrid / 2);
+      return -107;
+    }
+    err = cudaLaunchKernelEx(&cfg, moe_prefill_kernel, p);
+    if (err != cudaSuccess) {
+      fprintf(stderr, "kernel launch failed: %s\n", cudaGetErrorString(err));
+      return static_cast<int>(err);
+    }
+    return 0;
+  }
   moe_prefill_kernel<<<kGrid, BLOCK, DYN_SMEM, stream>>>(p);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
@@ -1571,7 +1713,7 @@ int launch_prefill_moe_wgmma_q1_ep2(const float* logits, int num_tokens, int blo
 // of both model families store it so) and logits_out a [T, E] fp32 buffer that receives the logits the
 // kernel routed on. Everything from num_tokens on is the argument list of the _ep2 entry.
 // -105: router_w_bf16 or logits_out is null.
-int prefill_wgmma_has_router_gemv() { return 1; }
+int prefill_wgmma_has_router_gemv() { return PAIR ? 0 : 1; }
 int launch_prefill_moe_wgmma_q1_gemv(const void* router_w_bf16, float* logits_out, int num_tokens, int block_m,
                                      void* workspace, size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
                                      float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
@@ -1673,7 +1815,7 @@ int launch_prefill_moe_wgmma_q1_ep(const float* logits, int num_tokens, int bloc
 //   the GPU (different streams, no ordering between them) race on it: serialise them.
 // * The first call on each device resolves the array's device address with cudaGetSymbolAddress
 //   (with that device current) and caches it; make that first call outside any stream capture.
-constexpr int kNoAllocMaxTokens = (H_DIM <= 2048) ? 256 : 64;
+constexpr int kNoAllocMaxTokens = (H_DIM <= 2048) ? 256 : (NCH > 1 ? 32 : 64);
 constexpr size_t na_align(size_t x) { return (x + 255) / 256 * 256; }
 constexpr size_t kNaWorkspace = 0;
 constexpr size_t kNaActFp8 = kNaWorkspace + na_align(sizeof(Workspace));
@@ -1682,7 +1824,7 @@ constexpr size_t kNaTopkIds = kNaActScales + na_align(static_cast<size_t>(kNoAll
 constexpr size_t kNaTopkW = kNaTopkIds + na_align(static_cast<size_t>(kNoAllocMaxTokens) * TOP_K * 4);
 constexpr size_t kNaSorted = kNaTopkW + na_align(static_cast<size_t>(kNoAllocMaxTokens) * TOP_K * 4);
 constexpr size_t kNaPartial = kNaSorted + na_align(static_cast<size_t>(kNoAllocMaxTokens) * TOP_K * 4);
-constexpr size_t kNaBytes = kNaPartial + na_align(static_cast<size_t>(kNoAllocMaxTokens) * TOP_K * H_DIM * 2);
+constexpr size_t kNaBytes = kNaPartial + na_align(static_cast<size_t>(kNoAllocMaxTokens) * TOP_K * NCH * H_DIM * 2);
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNaBytes];
 

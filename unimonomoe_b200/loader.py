@@ -210,7 +210,7 @@ class MonoKernel:
                 "topk_ids": torch.empty(M, k, dtype=torch.int32, device=device),
                 "topk_weights": torch.empty(M, k, dtype=torch.float32, device=device),
                 "sorted_ids": torch.empty(M * k, dtype=torch.int32, device=device),
-                "partial": torch.empty(M * k, H, dtype=torch.bfloat16, device=device),
+                "partial": torch.empty(M * k * (self._int_symbol("partial_chunks") or 1), H, dtype=torch.bfloat16, device=device),
             }
             if len(self._scratch) >= 4:
                 self._scratch.pop(next(iter(self._scratch)))
