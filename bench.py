@@ -441,7 +441,8 @@ def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flop
         "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
         "config": {"workload": f"{spec.name} MoE layer prefill, T={T} tokens, H={spec.hidden}, E=256, top-8, "
                                f"I={spec.inter}, block-FP8 [128,128] weights", "tokens": T, "parallelism": par, "variant": variant,
-                   "l2_policy": "inputs larger than L2: 805 MB of weights + 0.5 GB of partial rows stream per step",
+                   "l2_policy": (f"inputs larger than L2: {3 * 256 * spec.hidden * spec.inter / world / 1e6:.0f} MB of "
+                                 f"weights per rank + the partial rows stream every step"),
                    "reduce": reduce_desc,
                    "router": ("bf16 router linear inside the launch (its 2*T*H*E FLOPs are not counted)"
                               if args.router == "gemv" else "fp32 logits supplied by the caller")},
