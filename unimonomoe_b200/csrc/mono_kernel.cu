@@ -290,152 +290,200 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
 // descending score order, ties to the lower expert id, weights renormalised by their sum
 // (clamped at 1e-30); modes 1/2 select on sigmoid+bias and weight by the unbiased sigmoid.
 // A slot for which no selectable expert remains gets id -1 and weight 0.
-__device__ __forceinline__ void route_token(const float (&logit)[8], const float* __restrict__ bias, int lane,
-                                            int& my_id, float& my_w) {
-  float sel[8], unb[8];
-  float m = 0.f, s = 1.f;
+// NT tokens are routed side by side (every step loops over them) so that the shuffle / redux / division
+// latencies of one token are filled with the other's instructions; the arithmetic per token is unchanged.
+template <int NT>
+__device__ __forceinline__ void route_tokens(const float (&logit)[NT][8], const float* __restrict__ bias, int lane,
+                                             int (&my_id)[NT], float (&my_w)[NT]) {
+  float sel[NT][8], unb[NT][8];
+  float m[NT], s[NT];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) sel[j] = logit[j];
+  for (int a = 0; a < NT; ++a) {
+    m[a] = 0.f;
+    s[a] = 1.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sel[a][j] = logit[a][j];
+  }
   if constexpr (ROUTER_MODE == 0) {
-    m = sel[0];
 #pragma unroll
-    for (int j = 1; j < 8; ++j) m = fmaxf(m, sel[j]);
-    m = warp_max_f(m);
-    float part = 0.f;
+    for (int a = 0; a < NT; ++a) {
+      m[a] = sel[a][0];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) part += det_expf(sel[j] - m);
-    s = warp_sum_f(part);
+      for (int j = 1; j < 8; ++j) m[a] = fmaxf(m[a], sel[a][j]);
+    }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) unb[j] = sel[j];
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+      for (int a = 0; a < NT; ++a) m[a] = fmaxf(m[a], __shfl_xor_sync(0xFFFFFFFFu, m[a], off));
+    }
+    float part[NT];
+#pragma unroll
+    for (int a = 0; a < NT; ++a) {
+      part[a] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) part[a] += det_expf(sel[a][j] - m[a]);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+      for (int a = 0; a < NT; ++a) part[a] += __shfl_xor_sync(0xFFFFFFFFu, part[a], off);
+    }
+#pragma unroll
+    for (int a = 0; a < NT; ++a) {
+      s[a] = part[a];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) unb[a][j] = sel[a][j];
+    }
   } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float sg = det_sigmoidf(sel[j]);
-      unb[j] = sg;
-      sel[j] = (bias != nullptr) ? __fadd_rn(sg, bias[lane + 32 * j]) : sg;
-    }
-    if constexpr (ROUTER_MODE == 2) {
-      float gs[8];
+    for (int a = 0; a < NT; ++a) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        // top-1 (with its lane, ties to the lower lane) and top-2 of the group
-        const bool ok = sel[j] > -FLT_MAX;
-        unsigned long long k1 = ok ? ((static_cast<unsigned long long>(float_key(sel[j])) << 32) |
-                                      static_cast<unsigned long long>(31 - lane))
-                                   : 0ull;
-        k1 = warp_max_u64(k1);
-        const int l1 = 31 - static_cast<int>(k1 & 0xFFFFFFFFull);
-        const float b1 = __shfl_sync(0xFFFFFFFFu, sel[j], l1 & 31);
-        float b2 = (lane == l1 || !ok) ? -FLT_MAX : sel[j];
-        b2 = warp_max_f(b2);
-        gs[j] = (k1 == 0ull) ? -FLT_MAX : __fadd_rn(b1, b2);
+        const float sg = det_sigmoidf(sel[a][j]);
+        unb[a][j] = sg;
+        sel[a][j] = (bias != nullptr) ? __fadd_rn(sg, bias[lane + 32 * j]) : sg;
       }
-      uint32_t keep = 0u;
+    }
+    if constexpr (ROUTER_MODE == 2) {
 #pragma unroll
-      for (int r = 0; r < TOPK_GROUP; ++r) {
-        float gb = -FLT_MAX;
-        int gi = -1;
+      for (int a = 0; a < NT; ++a) {
+        float gs[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          // top-1 (with its lane, ties to the lower lane) and top-2 of the group
+          const bool ok = sel[a][j] > -FLT_MAX;
+          unsigned long long k1 = ok ? ((static_cast<unsigned long long>(float_key(sel[a][j])) << 32) |
+                                        static_cast<unsigned long long>(31 - lane))
+                                     : 0ull;
+          k1 = warp_max_u64(k1);
+          const int l1 = 31 - static_cast<int>(k1 & 0xFFFFFFFFull);
+          const float b1 = __shfl_sync(0xFFFFFFFFu, sel[a][j], l1 & 31);
+          float b2 = (lane == l1 || !ok) ? -FLT_MAX : sel[a][j];
+          b2 = warp_max_f(b2);
+          gs[j] = (k1 == 0ull) ? -FLT_MAX : __fadd_rn(b1, b2);
+        }
+        uint32_t keep = 0u;
+#pragma unroll
+        for (int r = 0; r < TOPK_GROUP; ++r) {
+          float gb = -FLT_MAX;
+          int gi = -1;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (!((keep >> j) & 1u) && gs[j] > gb) { gb = gs[j]; gi = j; }
+          if (gi >= 0) keep |= 1u << gi;
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          if (!((keep >> j) & 1u) && gs[j] > gb) { gb = gs[j]; gi = j; }
-        if (gi >= 0) keep |= 1u << gi;
+          if (!((keep >> j) & 1u)) sel[a][j] = -FLT_MAX;
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (!((keep >> j) & 1u)) sel[j] = -FLT_MAX;
     }
   }
 
-  // One 64-bit key per candidate, built once: orderable score in the high word, inverted expert id in
-  // the low word (ties fall to the lower id, and every key is unique). 0 = not selectable / taken.
-  unsigned long long key[8];
+  // One 32-bit orderable key per candidate, built once; 0 = not selectable / taken. A round takes the
+  // largest key of the warp (redux.sync.max) and, among the candidates that carry it, the lowest expert
+  // id (redux.sync.min): descending score, ties to the lower id.
+  uint32_t key[NT][8];
+  float wsum[NT];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float v = sel[j] + 0.0f;  // folds -0 into +0 so that the integer key orders exactly like operator>
-    key[j] = (v > -FLT_MAX) ? ((static_cast<unsigned long long>(float_key(v)) << 32) |
-                               static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<uint32_t>(lane + 32 * j)))
-                            : 0ull;
+  for (int a = 0; a < NT; ++a) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float v = sel[a][j] + 0.0f;  // folds -0 into +0 so that the integer key orders exactly like operator>
+      key[a][j] = (v > -FLT_MAX) ? float_key(v) : 0u;
+    }
+    wsum[a] = 0.f;
+    my_id[a] = -1;
+    my_w[a] = 0.f;
   }
-  float wsum = 0.f;
-  my_id = -1;
-  my_w = 0.f;
 #pragma unroll 1
   for (int k = 0; k < TOP_K; ++k) {
-    unsigned long long best = key[0];
+    uint32_t best[NT];
+    int bidx[NT];
+    float mine[NT], wk[NT];
 #pragma unroll
-    for (int j = 1; j < 8; ++j) best = key[j] > best ? key[j] : best;
-    best = warp_max_u64(best);
-    int bidx = -1;
-    float wk = 0.f;
-    if (best != 0ull) {
-      bidx = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(best & 0xFFFFFFFFull));
-      const int owner = bidx & 31, slot = bidx >> 5;
-      float mine = 0.f;
+    for (int a = 0; a < NT; ++a) {
+      const uint32_t m01 = max(key[a][0], key[a][1]), m23 = max(key[a][2], key[a][3]),
+                     m45 = max(key[a][4], key[a][5]), m67 = max(key[a][6], key[a][7]);
+      best[a] = __reduce_max_sync(0xFFFFFFFFu, max(max(m01, m23), max(m45, m67)));
+    }
+#pragma unroll
+    for (int a = 0; a < NT; ++a) {
+      uint32_t cand = 0xFFFFFFFFu;
+#pragma unroll
+      for (int j = 7; j >= 0; --j)
+        if (key[a][j] == best[a] && best[a] != 0u) cand = static_cast<uint32_t>(lane + 32 * j);
+      bidx[a] = static_cast<int>(__reduce_min_sync(0xFFFFFFFFu, cand));  // -1 when nothing is selectable
+    }
+#pragma unroll
+    for (int a = 0; a < NT; ++a) {
+      const int owner = bidx[a] & 31, slot = (bidx[a] >> 5) & 7;
+      mine[a] = 0.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        if (j == slot) {
-          mine = unb[j];
-          if (lane == owner) key[j] = 0ull;  // the owner retires the winner
+        if (j == slot && bidx[a] >= 0) {
+          mine[a] = unb[a][j];
+          if (lane == owner) key[a][j] = 0u;  // the owner retires the winner
         }
       }
-      const float bu = __shfl_sync(0xFFFFFFFFu, mine, owner);
-      wk = (ROUTER_MODE == 0) ? __fdiv_rn(det_expf(bu - m), s) : bu;
+      mine[a] = __shfl_sync(0xFFFFFFFFu, mine[a], owner);
     }
-    wsum += wk;
-    if (lane == k) { my_id = bidx; my_w = wk; }
+#pragma unroll
+    for (int a = 0; a < NT; ++a) {
+      wk[a] = 0.f;
+      if (bidx[a] >= 0) wk[a] = (ROUTER_MODE == 0) ? __fdiv_rn(det_expf(mine[a] - m[a]), s[a]) : mine[a];
+      wsum[a] += wk[a];
+      if (lane == k) { my_id[a] = bidx[a]; my_w[a] = wk[a]; }
+    }
   }
-  const float inv = __fdiv_rn(1.0f, fmaxf(wsum, 1e-30f));
-  my_w = __fmul_rn(my_w, inv);
+#pragma unroll
+  for (int a = 0; a < NT; ++a) {
+    const float inv = __fdiv_rn(1.0f, fmaxf(wsum[a], 1e-30f));
+    my_w[a] = __fmul_rn(my_w[a], inv);
+  }
 }
 
 // ------------------------------------------------------------------ phase 0.5: activation quantisation
 // bf16 -> e4m3 with one fp32 scale per (token, 128 columns): amax, inv = 448/amax,
 // q = e4m3_rn_satfinite(x * inv), scale = amax/448; amax < FLT_MIN is treated as 1
 // (kernel/qwen_tp/src/prefill_mono_final_nb.cu:1225-1244). A half-warp owns one group.
-__device__ __forceinline__ void quantize_activations(const Params& p, int gwarp, int nwarps, int lane) {
-  const long long ngroups = static_cast<long long>(p.num_tokens) * NK;
+// One token is quantised by one warp, in two steps so that the loads can be in flight while the
+// warp does something else (routing): half-warp `half` owns the 128-column groups 2*u + half, lane `sub`
+// of it the 16-byte piece `sub` of a group. A piece of work is QU groups per half-warp.
+constexpr int QU = 8;
+constexpr int Q_PIECES = (NK / 2 + QU - 1) / QU;
+__device__ __forceinline__ void quant_token_load(const Params& p, int tok, int piece, int lane, uint4 (&raw)[QU]) {
   const int half = lane >> 4, sub = lane & 15;
-  constexpr int U = 8;  // independent 16-byte loads in flight per lane
-  for (long long g0 = static_cast<long long>(gwarp) * 2 + half; g0 < ngroups;
-       g0 += static_cast<long long>(nwarps) * 2 * U) {
-    uint4 raw[U];
-    bool live[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long g = g0 + static_cast<long long>(nwarps) * 2 * u;
-      live[u] = g < ngroups;
-      raw[u] = make_uint4(0u, 0u, 0u, 0u);
-      if (live[u]) {
-        const long long tok = g / NK;
-        const int kb = static_cast<int>(g % NK);
-        raw[u] = *reinterpret_cast<const uint4*>(p.act_bf16 + tok * K_DIM + kb * 128 + sub * 8);
-      }
+  for (int u = 0; u < QU; ++u) {
+    const int kb = 2 * (piece * QU + u) + half;
+    raw[u] = make_uint4(0u, 0u, 0u, 0u);
+    if (kb < NK)
+      raw[u] = *reinterpret_cast<const uint4*>(p.act_bf16 + static_cast<size_t>(tok) * K_DIM + kb * 128 + sub * 8);
+  }
+}
+__device__ __forceinline__ void quant_token_store(const Params& p, int tok, int piece, int lane, const uint4 (&raw)[QU]) {
+  const int half = lane >> 4, sub = lane & 15;
+#pragma unroll
+  for (int u = 0; u < QU; ++u) {
+    const int kb = 2 * (piece * QU + u) + half;
+    const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&raw[u]);
+    float x[8];
+    float am = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      x[i] = __bfloat162float(b[i]);
+      am = fmaxf(am, fabsf(x[i]));
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long g = g0 + static_cast<long long>(nwarps) * 2 * u;
-      const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&raw[u]);
-      float x[8];
-      float am = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        x[i] = __bfloat162float(b[i]);
-        am = fmaxf(am, fabsf(x[i]));
-      }
-      // reduce inside the 16-lane half (all 32 lanes execute the shuffles)
-#pragma unroll
-      for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, off));
-      if (am < FLT_MIN) am = 1.f;
-      const float inv = __fdiv_rn(448.0f, am);
-      if (live[u]) {
-        const long long tok = g / NK;
-        const int kb = static_cast<int>(g % NK);
-        uint2 q;
-        q.x = pack_e4m3x4(__fmul_rn(x[0], inv), __fmul_rn(x[1], inv), __fmul_rn(x[2], inv), __fmul_rn(x[3], inv));
-        q.y = pack_e4m3x4(__fmul_rn(x[4], inv), __fmul_rn(x[5], inv), __fmul_rn(x[6], inv), __fmul_rn(x[7], inv));
-        *reinterpret_cast<uint2*>(p.act_fp8 + tok * K_DIM + kb * 128 + sub * 8) = q;
-        if (sub == 0) p.act_scales[tok * NK + kb] = __fdiv_rn(am, 448.0f);
-      }
+    for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, off));
+    if (am < FLT_MIN) am = 1.f;
+    const float inv = __fdiv_rn(448.0f, am);
+    if (kb < NK) {
+      uint2 q;
+      q.x = pack_e4m3x4(__fmul_rn(x[0], inv), __fmul_rn(x[1], inv), __fmul_rn(x[2], inv), __fmul_rn(x[3], inv));
+      q.y = pack_e4m3x4(__fmul_rn(x[4], inv), __fmul_rn(x[5], inv), __fmul_rn(x[6], inv), __fmul_rn(x[7], inv));
+      *reinterpret_cast<uint2*>(p.act_fp8 + static_cast<size_t>(tok) * K_DIM + kb * 128 + sub * 8) = q;
+      if (sub == 0) p.act_scales[static_cast<size_t>(tok) * NK + kb] = __fdiv_rn(am, 448.0f);
     }
   }
 }
@@ -616,37 +664,64 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
   for (int i = tid; i < NWARPS * E; i += BLOCK) hist[i] = 0;
   __syncthreads();
 
-  // Every warp first routes its range of tokens, then quantises activations. (Splitting the
-  // warps into routers and quantisers was measured and is slower: routing is instruction-bound and
-  // wants all twelve warps.)
+  // Every warp routes AND quantises its own tokens, one at a time: the first piece of the token's
+  // activations is requested before the routing arithmetic (a chain of warp shuffles that leaves most issue
+  // slots empty) and consumed after it, so the memory latency of the quantiser hides behind the router.
+  // (Splitting the warps into routers and quantisers was measured and is slower: routing wants all twelve.)
 
-  float lg_next[8];
+  constexpr int NT = 1;  // tokens routed side by side by one warp (two were measured: 8 % slower, the second token's state costs more than the filled latency gains)
+  float lg_next[NT][8];
   if (t_begin < t_end) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) lg_next[j] = lg_src[static_cast<size_t>(t_begin) * E + lane + 32 * j];
-  }
-  for (int t = t_begin; t < t_end; ++t) {
-    int my_id;
-    float my_w;
-    float lg[8];
+    for (int a = 0; a < NT; ++a) {
+      const int tt = min(t_begin + a, t_end - 1);  // an odd tail routes its last token twice and drops the copy
 #pragma unroll
-    for (int j = 0; j < 8; ++j) lg[j] = lg_next[j];
-    if (t + 1 < t_end) {  // the next token's logits are in flight while this one is routed
-#pragma unroll
-      for (int j = 0; j < 8; ++j) lg_next[j] = lg_src[static_cast<size_t>(t + 1) * E + lane + 32 * j];
+      for (int j = 0; j < 8; ++j) lg_next[a][j] = lg_src[static_cast<size_t>(tt) * E + lane + 32 * j];
     }
-    route_token(lg, p.router_bias, lane, my_id, my_w);
-    if (lane < TOP_K) {
-      int lid = my_id;
-      if constexpr (EP_BUILD) lid = (my_id >= 0) ? p.expert_map[my_id] : -1;
-      if (lid >= E_LOCAL) lid = -1;
-      p.topk_ids[t * TOP_K + lane] = lid;
-      p.topk_weights[t * TOP_K + lane] = my_w;
-      if (lid >= 0) hist[warp * E + lid] += 1;  // ids of one token are distinct: no conflict
+  }
+  for (int t = t_begin; t < t_end; t += NT) {
+    int my_id[NT];
+    float my_w[NT];
+    float lg[NT][8];
+    uint4 qraw[NT][QU];
+#pragma unroll
+    for (int a = 0; a < NT; ++a) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) lg[a][j] = lg_next[a][j];
+    }
+    if (t + NT < t_end) {  // the next tokens' logits are in flight while these are routed
+#pragma unroll
+      for (int a = 0; a < NT; ++a) {
+        const int tt = min(t + NT + a, t_end - 1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) lg_next[a][j] = lg_src[static_cast<size_t>(tt) * E + lane + 32 * j];
+      }
+    }
+#pragma unroll
+    for (int a = 0; a < NT; ++a)
+      if (t + a < t_end) quant_token_load(p, t + a, 0, lane, qraw[a]);
+    route_tokens<NT>(lg, p.router_bias, lane, my_id, my_w);
+#pragma unroll
+    for (int a = 0; a < NT; ++a) {
+      if (t + a >= t_end) break;
+      if (lane < TOP_K) {
+        int lid = my_id[a];
+        if constexpr (EP_BUILD) lid = (my_id[a] >= 0) ? p.expert_map[my_id[a]] : -1;
+        if (lid >= E_LOCAL) lid = -1;
+        p.topk_ids[(t + a) * TOP_K + lane] = lid;
+        p.topk_weights[(t + a) * TOP_K + lane] = my_w[a];
+        if (lid >= 0) hist[warp * E + lid] += 1;  // ids of one token are distinct: no conflict
+      }
+      __syncwarp();  // the next token's increments may hit the same counters from other lanes
+      quant_token_store(p, t + a, 0, lane, qraw[a]);
+#pragma unroll 1
+      for (int piece = 1; piece < Q_PIECES; ++piece) {
+        quant_token_load(p, t + a, piece, lane, qraw[a]);
+        quant_token_store(p, t + a, piece, lane, qraw[a]);
+      }
     }
     __syncwarp();
   }
-  quantize_activations(p, gwarp, nwarps_grid, lane);
   __syncthreads();
   if (tid < E) {
     int c = 0;
