@@ -255,7 +255,7 @@ def main() -> None:
     # 32 communication CTAs measured best on B200 (14, 32 and 48 tried at four ranks)
     os.environ.setdefault("VLLM_PREFILL_MONOKERNEL_TP_NCOMM", "32")
     if world > 1 and not args.unfused:
-        plan = tp_fused.FusedTPPlan(mk, dist.group.WORLD, hidden=spec.hidden, max_tokens=T)
+        plan = tp_fused.FusedTPPlan(mk, dist.group.WORLD, hidden=spec.hidden, max_tokens=T, nslots=2)
         if plan.usable and plan.chunks_for(T) == 0:
             plan.chunks_by_tokens[T] = 8 if T >= 16384 else 4
         if not plan.usable:
@@ -274,15 +274,16 @@ def main() -> None:
 
     def launch(hs, lg, dst=None):
         if plan is not None:
+            slot = 1 if (dst is not None and dst.data_ptr() == plan.pool.base_ptr(1)) else 0
             plan.fused_tp_launch(hs, lg, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k,
-                                 True, layer["bias"], expert_map=emap)
+                                 True, layer["bias"], expert_map=emap, slot=slot)
         else:
             mk.prefill_impl(hs, lg, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k, True,
                             layer["bias"], out if dst is None else dst, expert_map=emap, scratch=sc, router_weight=rw16)
 
-    def reduce_out():
+    def reduce_out(dst=None):
         if world > 1 and plan is None:
-            dist.all_reduce(out)
+            dist.all_reduce(out if dst is None else dst)
 
     def step():
         launch(batch["hs"], batch["logits"])
@@ -325,69 +326,95 @@ def main() -> None:
     e2e_ms = None
     if not args.kernel_only:
         result = plan.pool.output(T) if plan is not None else out
-        # a second output slot lets the next kernel run while the previous result is still going to the host;
-        # the fused reduce writes the one symmetric pool slot, and NCCL reduces `out` in place
-        second = torch.empty_like(out) if world == 1 else None
-        e2e_ms = time_e2e(args, spec, batch, result, launch, reduce_out, world, dist, barrier, dev,
+        # a second output slot (a second slot of the symmetric pool under the fused reduce) lets the next
+        # kernel run while the previous result is still going to the host
+        second = plan.pool.output(T, 1) if plan is not None else torch.empty_like(out)
+        e2e_ms = time_e2e(args, spec, batch, result, launch, reduce_out, world, rank, dist, barrier, dev,
                           with_logits=rw16 is None, second_out=second)
     h2d = batch["hs"].numel() * 2 + (batch["logits"].numel() * 4 if rw16 is None else 0)
     d2h = out.numel() * 2
 
     if rank == 0:
+        ph = mk.workspace_view(sc["workspace"])["phase_ns"].tolist()
+        phases = [round((ph[i + 1] - ph[i]) / 1e3, 1) for i in range(4)]
         report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
-               reduce_desc)
+               reduce_desc, phases)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
-def time_e2e(args, spec, batch, out, launch, reduce_out, world, dist, barrier, dev, with_logits=True,
+def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barrier, dev, with_logits=True,
              second_out=None) -> tuple:
     """End to end through the public API: host buffers in, host result out, every step's copies inside the
     timed region. Returns (ms per step with the steps software-pipelined, ms per step strictly serial).
 
     Pipelined: the upload of step i+1, the kernel of step i and the download of step i-1 run on three
     streams over two input slots (and two output slots when `second_out` is given; with one output slot the
-    next kernel waits for the download). Every step still moves its own inputs and its own result."""
+    next kernel waits for the download). Every step still moves its own inputs and its own result.
+
+    N > 1: the batch crosses PCIe once, not once per GPU. Rank r uploads rows [r*T/N, (r+1)*T/N) of the
+    hidden states and logits, an NCCL all-gather over NVLink completes them on every GPU (on the compute
+    stream, directly in front of the kernel: a collective that ran beside the persistent kernel could wait
+    for a peer whose GPU is occupied by that very kernel), and rank r downloads the same rows of the
+    reduced output."""
     T = batch["hs"].shape[0]
-    hs_host = batch["hs"].cpu().pin_memory()
-    lg_host = batch["logits"].cpu().pin_memory()
+    assert T % world == 0
+    rows = slice(rank * (T // world), (rank + 1) * (T // world))
+    hs_host = batch["hs"][rows].cpu().pin_memory()
+    lg_host = batch["logits"][rows].cpu().pin_memory()
     outs = [out] if second_out is None else [out, second_out]
-    out_host = [torch.empty(T, spec.hidden, dtype=torch.bfloat16).pin_memory() for _ in outs]
+    out_host = [torch.empty(T // world, spec.hidden, dtype=torch.bfloat16).pin_memory() for _ in outs]
     NB = 2
     hs_dev = [torch.empty_like(batch["hs"]) for _ in range(NB)]
     lg_dev = [torch.empty_like(batch["logits"]) for _ in range(NB)]
+    hs_part = [torch.empty_like(batch["hs"][rows]) for _ in range(NB)] if world > 1 else None
+    lg_part = [torch.empty_like(batch["logits"][rows]) for _ in range(NB)] if world > 1 else None
     cur = torch.cuda.current_stream()
     s_in, s_c, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
     ev_in = [torch.cuda.Event() for _ in range(NB)]     # upload of the slot finished
     ev_k = [torch.cuda.Event() for _ in range(NB)]      # the kernel that read the slot finished
     ev_o = [torch.cuda.Event() for _ in outs]           # download of the output slot finished
 
+    def upload(b):
+        if world == 1:
+            hs_dev[b].copy_(hs_host, non_blocking=True)
+            if with_logits:
+                lg_dev[b].copy_(lg_host, non_blocking=True)
+        else:
+            hs_part[b].copy_(hs_host, non_blocking=True)
+            if with_logits:
+                lg_part[b].copy_(lg_host, non_blocking=True)
+
+    def gather(b):
+        if world > 1:
+            dist.all_gather_into_tensor(hs_dev[b], hs_part[b])
+            if with_logits:
+                dist.all_gather_into_tensor(lg_dev[b], lg_part[b])
+
     def serial_step():
-        hs_dev[0].copy_(hs_host, non_blocking=True)
-        if with_logits:
-            lg_dev[0].copy_(lg_host, non_blocking=True)
+        upload(0)
+        gather(0)
         launch(hs_dev[0], lg_dev[0], outs[0])
-        reduce_out()
-        out_host[0].copy_(outs[0], non_blocking=True)
+        reduce_out(outs[0])
+        out_host[0].copy_(outs[0][rows], non_blocking=True)
 
     def piped_step(i):
         b, o = i % NB, i % len(outs)
         with torch.cuda.stream(s_in):
             s_in.wait_event(ev_k[b])
-            hs_dev[b].copy_(hs_host, non_blocking=True)
-            if with_logits:
-                lg_dev[b].copy_(lg_host, non_blocking=True)
+            upload(b)
             ev_in[b].record(s_in)
         with torch.cuda.stream(s_c):
             s_c.wait_event(ev_in[b])
             s_c.wait_event(ev_o[o])
+            gather(b)
             launch(hs_dev[b], lg_dev[b], outs[o])
-            reduce_out()
+            reduce_out(outs[o])
             ev_k[b].record(s_c)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_k[b])
-            out_host[o].copy_(outs[o], non_blocking=True)
+            out_host[o].copy_(outs[o][rows], non_blocking=True)
             ev_o[o].record(s_out)
 
     def timed(fn, n, piped):
@@ -420,7 +447,7 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, dist, barrier, d
 
 
 def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
-           reduce_desc) -> None:
+           reduce_desc, phases=None) -> None:
     peaks = measured_peaks()
     fp8_lib = fp8_gemm_tflops(dev) if (world == 1 and not args.kernel_only) else None
     if peaks.get("bf16_tflops"):
@@ -451,10 +478,15 @@ def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flop
                 {"value": flops / (e2e_ms[0] * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms[0],
                  "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                  "schedule": "steps software-pipelined over three streams (upload | kernel | download), two input "
-                             "slots; every step copies its own inputs and result",
+                             "slots; every step copies its own inputs and result"
+                             + ("" if world == 1 else f"; each rank moves 1/{world} of the rows over PCIe and an "
+                                "all-gather over NVLink completes the inputs on every GPU"),
                  "serial_ms_per_step": e2e_ms[1], "serial_value": flops / (e2e_ms[1] * 1e-3) / 1e12}),
         "gpu_launches": args.steps,
         "kernel_ms": kern_ms,
+        # the last launch on rank 0, from the kernel's own %globaltimer stamps: routing + quantisation,
+        # scan + scatter, expert pipeline, slot sum (+ in-kernel reduce)
+        "phases_us": phases,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                      "traffic": traffic, "peak_source": peak_src, "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
                      "library_fp8_gemm_tflops": fp8_lib},

@@ -1437,9 +1437,14 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       // Chunked one-shot all-reduce (kernel/qwen_tp/src/prefill_mono_final_nb.cu:1461-1504):
       // chunk c is split over world*ncomm shards aligned to 512 B; each shard is summed
       // across ranks by multimem.ld_reduce and written back to every rank by multimem.st.
+      // The communication CTAs work in two groups that take alternate chunks, so that the fixed cost of a
+      // chunk (ready wait, rank barrier over NVLink, filling and draining the load pipeline: ~15 us) of one
+      // group overlaps the transfer of the other.
       const int cb = bid - ncomp;
-      const int nsh = p.tp_world * p.tp_ncomm;
-      const int sh = p.tp_rank * p.tp_ncomm + cb;
+      const int ngroups = (p.tp_ncomm % 2 == 0 && nchunk >= 2) ? 2 : 1;
+      const int grp = cb % ngroups, ci = cb / ngroups, per_group = p.tp_ncomm / ngroups;
+      const int nsh = p.tp_world * per_group;
+      const int sh = p.tp_rank * per_group + ci;
       const size_t out_mv = static_cast<size_t>(T) * H_DIM / 8;
       constexpr size_t ALIGN = 32;
       bool ok = true;
@@ -1463,7 +1468,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         }
         return true;
       };
-      for (int c = 0; c < nchunk; ++c) {
+      for (int c = grp; c < nchunk; c += ngroups) {
         if (tid == 0) {
           ok = wait_counter_ge(&ws->tp_ready[c], static_cast<uint32_t>(ncomp), wc, kErrChunkReady, static_cast<uint32_t>(c));
           if (ok) ok = rank_barrier(c * p.tp_ncomm + cb);
@@ -1478,7 +1483,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         size_t s_lo = lo + (ng * sh / nsh) * ALIGN, s_hi = lo + (ng * (sh + 1) / nsh) * ALIGN;
         s_lo = s_lo < hi ? s_lo : hi;
         s_hi = s_hi < hi ? s_hi : hi;
-        constexpr int UN = 8;  // 16-byte reduce-loads in flight per thread: NVLink latency is covered by depth
+        constexpr int UN = 8;  // 16-byte reduce-loads in flight per thread (16 measured: no difference)
         for (size_t base = s_lo + tid; base < s_hi; base += static_cast<size_t>(UN) * BLOCK) {
           uint32_t x[UN][4];
           bool live[UN];
