@@ -443,7 +443,17 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barr
     serial_ms = timed(serial_step, n_e2e, False)
     timed(piped_step, 4, True)
     piped_ms = timed(piped_step, n_e2e, True)
-    return piped_ms, serial_ms
+    gather_ms = 0.0
+    if world > 1:   # the all-gather alone, for the record
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        g0.record()
+        for _ in range(5):
+            gather(0)
+        g1.record()
+        barrier()
+        gather_ms = g0.elapsed_time(g1) / 5
+    return piped_ms, serial_ms, gather_ms
 
 
 def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
@@ -481,7 +491,8 @@ def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flop
                              "slots; every step copies its own inputs and result"
                              + ("" if world == 1 else f"; each rank moves 1/{world} of the rows over PCIe and an "
                                 "all-gather over NVLink completes the inputs on every GPU"),
-                 "serial_ms_per_step": e2e_ms[1], "serial_value": flops / (e2e_ms[1] * 1e-3) / 1e12}),
+                 "serial_ms_per_step": e2e_ms[1], "serial_value": flops / (e2e_ms[1] * 1e-3) / 1e12,
+                 "allgather_ms": e2e_ms[2]}),
         "gpu_launches": args.steps,
         "kernel_ms": kern_ms,
         # the last launch on rank 0, from the kernel's own %globaltimer stamps: routing + quantisation,
