@@ -203,6 +203,9 @@ def main() -> None:
     ap.add_argument("--router", default="logits", choices=["logits", "gemv"],
                     help="logits: the caller's router logits go in (the reference's interface); gemv: the bf16 gate "
                          "weight goes in and the router linear runs inside the launch (no logits cross PCIe in e2e)")
+    ap.add_argument("--gather", default="nccl", choices=["nccl", "multimem"],
+                    help="N>1, e2e leg: how the row shards uploaded by the ranks are completed on every GPU: NCCL "
+                         "all-gather, or multimem stores into symmetric buffers (measured equal at 2 GPUs)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end leg, the library GEMM probe and the CPU baseline (profiling runs)")
     args = ap.parse_args()
@@ -354,7 +357,8 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barr
     next kernel waits for the download). Every step still moves its own inputs and its own result.
 
     N > 1: the batch crosses PCIe once, not once per GPU. Rank r uploads rows [r*T/N, (r+1)*T/N) of the
-    hidden states and logits, an NCCL all-gather over NVLink completes them on every GPU (on the compute
+    hidden states and logits, an all-gather over NVLink (multimem stores into symmetric buffers, or NCCL
+    where there is no multicast) completes them on every GPU (on the compute
     stream, directly in front of the kernel: a collective that ran beside the persistent kernel could wait
     for a peer whose GPU is occupied by that very kernel), and rank r downloads the same rows of the
     reduced output."""
@@ -366,8 +370,32 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barr
     outs = [out] if second_out is None else [out, second_out]
     out_host = [torch.empty(T // world, spec.hidden, dtype=torch.bfloat16).pin_memory() for _ in outs]
     NB = 2
-    hs_dev = [torch.empty_like(batch["hs"]) for _ in range(NB)]
-    lg_dev = [torch.empty_like(batch["logits"]) for _ in range(NB)]
+    gather_kind = "none"
+    if world > 1:
+        # the gathered inputs live in symmetric memory when the platform offers multicast, so that the
+        # all-gather is one multimem store per element instead of a ring of copies
+        try:
+            if args.gather == "nccl":
+                raise RuntimeError("NCCL all-gather selected")
+            import torch.distributed._symmetric_memory as sm
+            gname = dist.group.WORLD.group_name
+            hs_dev = [sm.empty(batch["hs"].shape, dtype=batch["hs"].dtype, device=dev) for _ in range(NB)]
+            lg_dev = [sm.empty(batch["logits"].shape, dtype=batch["logits"].dtype, device=dev) for _ in range(NB)]
+            for t in hs_dev + lg_dev:
+                if not int(sm.rendezvous(t, gname).multicast_ptr):
+                    raise RuntimeError("no multicast pointer")
+            gather_kind = "multimem"
+        except Exception as ex:  # plain device buffers and NCCL instead
+            if rank == 0 and args.gather != "nccl":
+                print(f"# symmetric all-gather unavailable ({ex}); using NCCL", file=sys.stderr)
+            gather_kind = "nccl"
+        ok = torch.tensor([1 if gather_kind == "multimem" else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)   # every rank must take the same path
+        if int(ok.item()) == 0:
+            gather_kind = "nccl"
+    if gather_kind != "multimem":
+        hs_dev = [torch.empty_like(batch["hs"]) for _ in range(NB)]
+        lg_dev = [torch.empty_like(batch["logits"]) for _ in range(NB)]
     hs_part = [torch.empty_like(batch["hs"][rows]) for _ in range(NB)] if world > 1 else None
     lg_part = [torch.empty_like(batch["logits"][rows]) for _ in range(NB)] if world > 1 else None
     cur = torch.cuda.current_stream()
@@ -387,7 +415,11 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barr
                 lg_part[b].copy_(lg_host, non_blocking=True)
 
     def gather(b):
-        if world > 1:
+        if gather_kind == "multimem":
+            torch.ops.symm_mem.multimem_all_gather_out(hs_part[b], gname, hs_dev[b])
+            if with_logits:
+                torch.ops.symm_mem.multimem_all_gather_out(lg_part[b], gname, lg_dev[b])
+        elif world > 1:
             dist.all_gather_into_tensor(hs_dev[b], hs_part[b])
             if with_logits:
                 dist.all_gather_into_tensor(lg_dev[b], lg_part[b])
@@ -453,7 +485,7 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barr
         g1.record()
         barrier()
         gather_ms = g0.elapsed_time(g1) / 5
-    return piped_ms, serial_ms, gather_ms
+    return piped_ms, serial_ms, gather_ms, gather_kind
 
 
 def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
@@ -492,7 +524,7 @@ def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flop
                              + ("" if world == 1 else f"; each rank moves 1/{world} of the rows over PCIe and an "
                                 "all-gather over NVLink completes the inputs on every GPU"),
                  "serial_ms_per_step": e2e_ms[1], "serial_value": flops / (e2e_ms[1] * 1e-3) / 1e12,
-                 "allgather_ms": e2e_ms[2]}),
+                 "allgather_ms": e2e_ms[2], "allgather": e2e_ms[3]}),
         "gpu_launches": args.steps,
         "kernel_ms": kern_ms,
         # the last launch on rank 0, from the kernel's own %globaltimer stamps: routing + quantisation,
