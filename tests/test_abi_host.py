@@ -185,3 +185,15 @@ def test_synthetic_shards_are_slices_of_one_layer():
     assert torch.equal(ep1["w13"].view(torch.uint8), full["w13"].view(torch.uint8)[2:6])
     m = synth.expert_map(spec, 1, 2)
     assert m.tolist() == [-1, -1, -1, -1, 0, 1, 2, 3]
+
+
+def test_router_weight_preparation():
+    """The in-kernel router takes the gate weight in bf16: a weight that is bf16-representable converts
+    exactly (the checkpoints' case), anything else is refused instead of silently changing the logits."""
+    from unimonomoe_b200.loader import prepare_router_weight
+    w = (torch.randn(256, 64) * 0.02).to(torch.bfloat16)
+    out = prepare_router_weight(w.float())
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and torch.equal(out, w)
+    assert prepare_router_weight(w) is not None
+    with pytest.raises(ValueError):
+        prepare_router_weight(torch.randn(256, 64) * 0.02)

@@ -118,3 +118,38 @@ def test_quant_act_matches_torch_restatement(oracle):
     ref_q = (xf * inv[..., None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).view(37, 256)
     assert (torch.from_numpy(s) == ref_s).all()
     assert (torch.from_numpy(q) == ref_q).all()
+
+
+def test_chunked_intermediate_is_the_same_layer(oracle):
+    """A wide intermediate processed in column chunks (one bf16 partial row per chunk, as the kernel does
+    beyond 512 columns) is the same computation up to the extra bf16 roundings: the chunk rows of a slot
+    add up to the unchunked row, and the outputs agree to bf16 accuracy. A chunk width that covers the whole
+    intermediate reproduces the unchunked result bit for bit."""
+    rs = np.random.RandomState(7)
+    E, K, H, NH, T, k = 4, 128, 128, 256, 16, 2
+
+    def e4m3_bytes(*shape):
+        b = rs.randint(0, 256, size=shape).astype(np.uint8)
+        b[(b & 0x7F) == 0x7F] = 0x38          # no NaN encodings
+        return b
+
+    w13, w2 = e4m3_bytes(E, 2 * NH, K), e4m3_bytes(E, H, NH)
+    s13 = (rs.rand(E, 2 * NH // 128, K // 128).astype(np.float32) + 0.5) * 1e-3
+    s2 = (rs.rand(E, H // 128, NH // 128).astype(np.float32) + 0.5) * 1e-3
+    hs = torch.from_numpy(rs.randn(T, K).astype(np.float32)).to(torch.bfloat16)
+    q, s = oracle.quant_act(hs)
+    ids = np.stack([rs.permutation(E)[:k] for _ in range(T)]).astype(np.int32)
+    w = rs.rand(T, k).astype(np.float32)
+    w /= w.sum(1, keepdims=True)
+    toks = np.arange(T)
+    whole, p_whole, *_ = oracle.moe_path(toks, q, s, ids, w, w13, s13, w2, s2, want_dumps=True, chunk_cols=512)
+    again = oracle.moe_path(toks, q, s, ids, w, w13, s13, w2, s2, chunk_cols=NH)
+    assert torch.equal(whole.view(torch.int16), again.view(torch.int16))
+    chunked, p_chunk, *_ = oracle.moe_path(toks, q, s, ids, w, w13, s13, w2, s2, want_dumps=True, chunk_cols=128)
+    assert p_whole.shape == (T * k, H) and p_chunk.shape == (T * k * 2, H)
+    rows = p_chunk.float().view(T * k, 2, H).sum(1)
+    scale = float(p_whole.float().abs().max())
+    assert float((rows - p_whole.float()).abs().max()) <= 2 ** -7 * scale
+    # two bf16 results of slightly different fp32 sums may differ by one bf16 step of the largest outputs
+    m = oracle.parity_metrics(chunked.float(), whole.float())
+    assert m["rel_l2"] < 5e-3 and m["cos"] > 0.9999, m
