@@ -21,6 +21,9 @@
 //             parallelism the last `ncomm` CTAs instead run a chunked one-shot
 //             all-reduce through the NVLS multicast alias while the others compute.
 //
+// An intermediate wider than 512 columns is processed in chunks of 512 (one partial row per chunk);
+// -DMONO_PAIR=1 schedules pairs of tiles on clusters of two CTAs (tcgen05 cta_group::2).
+//
 // What it replaces in the reference (same semantics, different machine):
 //   kernel/qwen_tp/src/prefill_mono_final_nb.cu:932-1506 (device kernel),
 //   :1513-1791 (host launcher and accessors), kernel/qwen_ep/src/...:1185-1207,
