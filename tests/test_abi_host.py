@@ -197,3 +197,19 @@ def test_router_weight_preparation():
     assert prepare_router_weight(w) is not None
     with pytest.raises(ValueError):
         prepare_router_weight(torch.randn(256, 64) * 0.02)
+
+
+def test_token_cap_is_enforced_before_any_cuda_call(built_libs, monkeypatch):
+    """More tokens than the cap (30720, the reference's MOE_MONOKERNEL_PREFILL_MAX_TOKENS) are refused by
+    the host module; the library's own bound on the tile list (-102) sits above it."""
+    mk = MonoKernel(built_libs["qwen_w1"])
+    assert loader.MOE_MONOKERNEL_PREFILL_MAX_TOKENS == 30720
+    assert (30720 * 8 // 128 + 256) <= mk.geometry()["max_tiles"]
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+
+    class FakeCuda(torch.Tensor):
+        is_cuda = True
+
+    x = torch.empty(30721, 2048, dtype=torch.bfloat16).as_subclass(FakeCuda)
+    with pytest.raises(RuntimeError, match="refuses 30721 tokens"):
+        mk.prefill_impl(x, None, None, None, torch.empty(256, 2048, 512), None, 8, True, None, None)

@@ -46,7 +46,7 @@ def ep_shard(full, rank, world):
     return {k: (full[k][sl].contiguous() if k in ("w13", "w13_scale", "w2", "w2_scale") else full[k]) for k in full}
 
 
-@pytest.mark.parametrize("T", [1, 7, 256, 1000, 8192, 16384])
+@pytest.mark.parametrize("T", [1, 7, 256, 1000, 8192, 16384, 30720])   # 30720: the loader's cap
 def test_qwen_single_gpu_parity(gu, oracle, qwen_full, T):
     mk = gu.kernel("qwen_w1")
     batch = synth.make_batch(synth.QWEN, qwen_full, T, seed=0, device=gu.DEV)
@@ -365,7 +365,7 @@ def _fp64_topk_margin(scores64, k=8):
     return (top[:, k - 1] - top[:, k])
 
 
-@pytest.mark.parametrize("T", [1, 1000, 16384])
+@pytest.mark.parametrize("T", [1, 1000, 16384, 30720])   # 30720: two token tiles per CTA in the router phase
 def test_router_linear_inside_the_launch(gu, oracle, qwen_full, T):
     """The _gemv entry computes logits = x * W_r^T (bf16 operands, fp32 accumulation on the tensor cores)
     for the tokens each CTA routes and routes on them in the same launch. Its accumulation order inside
