@@ -514,6 +514,7 @@ struct __align__(16) SharedState {
   int total_tiles;
   TileInfo tiles[MAX_MY_TILES];
   float rowmax[2][EPI_WGS][TILE_M];
+  alignas(16) int gather_tok[2][8][TILE_M / 8];  // token of row gr + 8 i of the tile being gathered, [tile parity][gr][i]
 };
 static_assert(sizeof(SharedState) <= SMEM_STATIC_RESERVE, "static shared state exceeds its reserve");
 
@@ -1051,10 +1052,66 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       }
     } else {
       // ---------------------------------------------------------- activation gather (warps 2-3, 64 threads)
-      // cp.async 16 B with the 128-byte swizzle applied by hand; thread g copies rows g and g+64.
+      // cp.async 16 B with the 128-byte swizzle applied by hand.
       // (TMA tile::gather4 was measured here as well: correct, but a third slower than this path
       // because every gathered row is a separate 128-byte request.)
       const int gt = tid - WARP_GATHER0 * 32;
+#ifndef MONO_GATHER_ROWWISE
+      // Eight neighbouring lanes copy the eight 16-byte pieces of ONE row, so a warp instruction touches
+      // 4 whole lines of global memory and 512 contiguous bytes of shared memory (one row per lane would be
+      // 32 lines per instruction and a 4-way bank conflict). Thread g: piece g % 8 of rows g / 8 + 8 i.
+      const int gc = gt & 7, gr = gt >> 3;
+      constexpr int ROWS_PER_THREAD = TILE_M / 8;
+      uint32_t na = 0;
+      bool dead = false;  // after an abort: keep the loop structure (the named barrier stays matched), skip the work
+      PROF_DECL(pg_emptyA);
+      const uint32_t a_ring_u32 = smem_u32(a_ring);
+      for (int it = 0; it < n_my; ++it) {
+        const TileInfo ti = S.tiles[it];
+        // the tile's 128 source tokens go through shared memory (two rows looked up per thread); the two
+        // buffers alternate by tile, and the barrier of tile it+1 separates the last read of tile it-1's
+        // buffer from its next fill
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int r = gt + hh * 64;
+          int t = -1;
+          if (r < ti.rows) {
+            const int fi = __ldcg(&p.sorted_ids[ti.row0 + r]);
+            if (fi >= 0 && fi < numel) t = fi / TOP_K;
+          }
+          S.gather_tok[it & 1][r & 7][r >> 3] = t;
+        }
+        named_bar_sync(2, N_GATHER);
+        for (int s = 0; s < NP * NK; ++s) {
+          const int ks = s % NK;
+          const uint32_t sa = na % SA;
+          { PROF_T0();
+          if (!dead && !mbar_wait(&S.emptyA[sa], ((na / SA) & 1u) ^ 1u, wc, kSiteEmptyA)) dead = true;
+          PROF_ADD(pg_emptyA); }
+          if (dead) continue;
+          // row gr + 8 i sits in eight-row group i (1024 bytes each) at row position gr, piece gc ^ gr
+          const uint32_t dst = a_ring_u32 + sa * A_STAGE_BYTES + gr * 128 + ((gc ^ gr) << 4);
+          const uint8_t* g0 = p.act_fp8 + ks * 128 + gc * 16;
+          if constexpr ((MONO_ABLATE & 8) == 0) {
+#pragma unroll
+            for (int i4 = 0; i4 < ROWS_PER_THREAD / 4; ++i4) {
+              const int4 t4 = *reinterpret_cast<const int4*>(&S.gather_tok[it & 1][gr][4 * i4]);
+              const int tok[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                if (tok[i] >= 0) cp_async16(dst + (4 * i4 + i) * 1024, g0 + static_cast<size_t>(tok[i]) * K_DIM);
+            }
+          }
+          // the barrier receives this thread's arrival when the copies above have landed
+          cp_async_arrive_noinc(&S.fullA[sa]);
+          ++na;
+        }
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
+      if (gt == 0) { PROF_STORE(6, pg_emptyA); }
+#else
+      // one row per lane: thread g copies rows g and g+64
       uint32_t na = 0;
       bool ok = true;
       PROF_DECL(pg_emptyA);
@@ -1094,6 +1151,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       cp_async_commit();
       cp_async_wait<0>();
       if (gt == 0) { PROF_STORE(6, pg_emptyA); }
+#endif
     }
   } else {
     // ------------------------------------------------------------ epilogue (EPI_WGS x 128 threads)
@@ -1320,6 +1378,39 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             }
           }
           PROF_T0();
+#ifndef MONO_ST_ROWWISE
+          // Neighbouring lanes swap half of their 32-byte pieces first, so that in every store instruction
+          // lanes 2i and 2i+1 write 64 contiguous bytes of ONE row: 16 lines per instruction instead of 32.
+          // (the guard is made warp-uniform: the shuffles below need every lane of the warp)
+          if (!__any_sync(0xFFFFFFFFu, dead) && (MONO_ABLATE & 4) == 0) {
+            static_assert(NSPLIT == 1, "the paired store is written for one accumulator buffer per slab");
+            const bool odd = (lane & 1) != 0;
+            const int fi_even = __shfl_sync(0xFFFFFFFFu, fi, lane & ~1), fi_odd = __shfl_sync(0xFFFFFFFFu, fi, lane | 1);
+            __nv_bfloat16* dst_even = p.partial + (static_cast<size_t>(fi_even < 0 ? 0 : fi_even) * NCH + ti.chunk) * H_DIM + hb * 256 + h * WC;
+            __nv_bfloat16* dst_odd = p.partial + (static_cast<size_t>(fi_odd < 0 ? 0 : fi_odd) * NCH + ti.chunk) * H_DIM + hb * 256 + h * WC;
+#pragma unroll
+            for (int k2 = 0; k2 < WC / 32; ++k2) {   // pieces 2*k2 and 2*k2+1 of this thread's WC columns
+              uint32_t lo[8], hi[8], mine[8], theirs[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float2 a = __fmul2_rn(acc[(2 * k2) * 8 + i], rw2), b = __fmul2_rn(acc[(2 * k2 + 1) * 8 + i], rw2);
+                lo[i] = cvt_bf16x2_satfinite(a.x, a.y);
+                hi[i] = cvt_bf16x2_satfinite(b.x, b.y);
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                // an even lane keeps its piece 2*k2 and gives away 2*k2+1; an odd lane the other way round
+                const uint32_t send = odd ? lo[i] : hi[i];
+                theirs[i] = __shfl_xor_sync(0xFFFFFFFFu, send, 1);
+                mine[i] = odd ? hi[i] : lo[i];
+              }
+              const int piece = 2 * k2 + (odd ? 1 : 0);
+              // row of the even lane: its own piece from the even lane, the received one from the odd lane
+              if (fi_even >= 0) st_global_256_stream(dst_even + piece * 16, odd ? theirs : mine);
+              if (fi_odd >= 0) st_global_256_stream(dst_odd + piece * 16, odd ? mine : theirs);
+            }
+          }
+#else
           if (fi >= 0 && !dead && (MONO_ABLATE & 4) == 0) {
 #pragma unroll
             for (int j = 0; j < NSPLIT; ++j) {
@@ -1339,6 +1430,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               }
             }
           }
+#endif
           if (has_next && hb >= 1 && hb - 1 < AS_PIECES) as_piece_store(hb - 1);
           PROF_ADD(pe_store);
         }
