@@ -402,7 +402,7 @@ __device__ __forceinline__ void route_tokens(const float (&logit)[NT][8], const 
   for (int k = 0; k < TOP_K; ++k) {
     uint32_t best[NT];
     int bidx[NT];
-    float mine[NT], wk[NT];
+    float mine[NT];
 #pragma unroll
     for (int a = 0; a < NT; ++a) {
       const uint32_t m01 = max(key[a][0], key[a][1]), m23 = max(key[a][2], key[a][3]),
@@ -429,19 +429,22 @@ __device__ __forceinline__ void route_tokens(const float (&logit)[NT][8], const 
         }
       }
       mine[a] = __shfl_sync(0xFFFFFFFFu, mine[a], owner);
-    }
-#pragma unroll
-    for (int a = 0; a < NT; ++a) {
-      wk[a] = 0.f;
-      if (bidx[a] >= 0) wk[a] = (ROUTER_MODE == 0) ? __fdiv_rn(det_expf(mine[a] - m[a]), s[a]) : mine[a];
-      wsum[a] += wk[a];
-      if (lane == k) { my_id[a] = bidx[a]; my_w[a] = wk[a]; }
+      // lane k keeps the k-th winner and its unbiased score; the weights are formed after the loop, by the
+      // eight lanes at once instead of one exponential and one division per round
+      if (lane == k) { my_id[a] = bidx[a]; my_w[a] = mine[a]; }
     }
   }
 #pragma unroll
   for (int a = 0; a < NT; ++a) {
+    float wk = 0.f;
+    if (lane < TOP_K && my_id[a] >= 0)
+      wk = (ROUTER_MODE == 0) ? __fdiv_rn(det_expf(my_w[a] - m[a]), s[a]) : my_w[a];
+    // the sum runs over the slots in ascending order, as a sequential accumulation would
+    wsum[a] = 0.f;
+#pragma unroll
+    for (int k = 0; k < TOP_K; ++k) wsum[a] += __shfl_sync(0xFFFFFFFFu, wk, k);
     const float inv = __fdiv_rn(1.0f, fmaxf(wsum[a], 1e-30f));
-    my_w[a] = __fmul_rn(my_w[a], inv);
+    my_w[a] = __fmul_rn(wk, inv);
   }
 }
 
@@ -1383,31 +1386,36 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
           // lanes 2i and 2i+1 write 64 contiguous bytes of ONE row: 16 lines per instruction instead of 32.
           // (the guard is made warp-uniform: the shuffles below need every lane of the warp)
           if (!__any_sync(0xFFFFFFFFu, dead) && (MONO_ABLATE & 4) == 0) {
-            static_assert(NSPLIT == 1, "the paired store is written for one accumulator buffer per slab");
             const bool odd = (lane & 1) != 0;
             const int fi_even = __shfl_sync(0xFFFFFFFFu, fi, lane & ~1), fi_odd = __shfl_sync(0xFFFFFFFFu, fi, lane | 1);
-            __nv_bfloat16* dst_even = p.partial + (static_cast<size_t>(fi_even < 0 ? 0 : fi_even) * NCH + ti.chunk) * H_DIM + hb * 256 + h * WC;
-            __nv_bfloat16* dst_odd = p.partial + (static_cast<size_t>(fi_odd < 0 ? 0 : fi_odd) * NCH + ti.chunk) * H_DIM + hb * 256 + h * WC;
+            __nv_bfloat16* row_even = p.partial + (static_cast<size_t>(fi_even < 0 ? 0 : fi_even) * NCH + ti.chunk) * H_DIM + hb * 256 + h * WC;
+            __nv_bfloat16* row_odd = p.partial + (static_cast<size_t>(fi_odd < 0 ? 0 : fi_odd) * NCH + ti.chunk) * H_DIM + hb * 256 + h * WC;
 #pragma unroll
-            for (int k2 = 0; k2 < WC / 32; ++k2) {   // pieces 2*k2 and 2*k2+1 of this thread's WC columns
-              uint32_t lo[8], hi[8], mine[8], theirs[8];
+            for (int j = 0; j < NSPLIT; ++j) {
+              __nv_bfloat16* dst_even = row_even + j * BC;
+              __nv_bfloat16* dst_odd = row_odd + j * BC;
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float2 a = __fmul2_rn(acc[(2 * k2) * 8 + i], rw2), b = __fmul2_rn(acc[(2 * k2 + 1) * 8 + i], rw2);
-                lo[i] = cvt_bf16x2_satfinite(a.x, a.y);
-                hi[i] = cvt_bf16x2_satfinite(b.x, b.y);
+              for (int k2 = 0; k2 < WC / 32; ++k2) {   // pieces 2*k2 and 2*k2+1 of this thread's WC columns of buffer j
+                uint32_t lo[8], hi[8], mine[8], theirs[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float2 a = __fmul2_rn(acc[j * (WC / 2) + (2 * k2) * 8 + i], rw2);
+                  const float2 b = __fmul2_rn(acc[j * (WC / 2) + (2 * k2 + 1) * 8 + i], rw2);
+                  lo[i] = cvt_bf16x2_satfinite(a.x, a.y);
+                  hi[i] = cvt_bf16x2_satfinite(b.x, b.y);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  // an even lane keeps its piece 2*k2 and gives away 2*k2+1; an odd lane the other way round
+                  const uint32_t send = odd ? lo[i] : hi[i];
+                  theirs[i] = __shfl_xor_sync(0xFFFFFFFFu, send, 1);
+                  mine[i] = odd ? hi[i] : lo[i];
+                }
+                const int piece = 2 * k2 + (odd ? 1 : 0);
+                // row of the even lane: its own piece from the even lane, the received one from the odd lane
+                if (fi_even >= 0) st_global_256_stream(dst_even + piece * 16, odd ? theirs : mine);
+                if (fi_odd >= 0) st_global_256_stream(dst_odd + piece * 16, odd ? mine : theirs);
               }
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                // an even lane keeps its piece 2*k2 and gives away 2*k2+1; an odd lane the other way round
-                const uint32_t send = odd ? lo[i] : hi[i];
-                theirs[i] = __shfl_xor_sync(0xFFFFFFFFu, send, 1);
-                mine[i] = odd ? hi[i] : lo[i];
-              }
-              const int piece = 2 * k2 + (odd ? 1 : 0);
-              // row of the even lane: its own piece from the even lane, the received one from the odd lane
-              if (fi_even >= 0) st_global_256_stream(dst_even + piece * 16, odd ? theirs : mine);
-              if (fi_odd >= 0) st_global_256_stream(dst_odd + piece * 16, odd ? mine : theirs);
             }
           }
 #else
