@@ -42,9 +42,9 @@ VARIANTS = {
 # development variants (not built by default): other epilogue shapes, and the stall-counter build
 DEV_VARIANTS = {
     "qwen_w1_n2": dict(QWEN, N_HALF=512, E_LOCAL=256, EPI_WGS=2, NSPLIT=2),
-    "qwen_w1_e4": dict(QWEN, N_HALF=512, E_LOCAL=256, EPI_WGS=4, NSPLIT=1),
     "qwen_w1_prof": dict(QWEN, N_HALF=512, E_LOCAL=256, PROFILE=1),
     "qwen_w1_plainst": dict(QWEN, N_HALF=512, E_LOCAL=256, PLAIN_STORES=1),
+    # A/B switches behind the measured numbers: one row per lane in the partial-row stores / in the gather
     "qwen_w1_strow": dict(QWEN, N_HALF=512, E_LOCAL=256, ST_ROWWISE=1),
     "qwen_w1_garow": dict(QWEN, N_HALF=512, E_LOCAL=256, GATHER_ROWWISE=1),
     "qwen_w1_old": dict(QWEN, N_HALF=512, E_LOCAL=256, GATHER_ROWWISE=1, ST_ROWWISE=1),
