@@ -206,6 +206,10 @@ def main() -> None:
     ap.add_argument("--gather", default="nccl", choices=["nccl", "multimem"],
                     help="N>1, e2e leg: how the row shards uploaded by the ranks are completed on every GPU: NCCL "
                          "all-gather, or multimem stores into symmetric buffers (measured equal at 2 GPUs)")
+    ap.add_argument("--variant", default=None,
+                    help="N=1 only: time another binary of the same geometry, e.g. a development build made with "
+                         "`python -m unimonomoe_b200.build qwen_w1_prof` (stall counters) or qwen_w1_abl7 (a piece of "
+                         "the work left out: wrong results, used to split the run time)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end leg, the library GEMM probe and the CPU baseline (profiling runs)")
     args = ap.parse_args()
@@ -235,7 +239,7 @@ def main() -> None:
         n = spec.inter // world
         kw = {"inter_slice": (rank * n, (rank + 1) * n), "chunk": 8}
     elif world == 1:
-        variant, par, kw = "qwen_w1", "none", {}
+        variant, par, kw = (args.variant or "qwen_w1"), "none", {}
     elif world in (2, 4) and args.parallel == "tp":
         variant, par = f"qwen_tp{world}", f"tp{world}"
         n = spec.inter // world
@@ -340,11 +344,31 @@ def main() -> None:
     if rank == 0:
         ph = mk.workspace_view(sc["workspace"])["phase_ns"].tolist()
         phases = [round((ph[i + 1] - ph[i]) / 1e3, 1) for i in range(4)]
+        stall_counters(mk, sc["workspace"])
         report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
                reduce_desc, phases)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+PROF_NAMES = ["tma_wait_emptyB", "mma_wait_fullB", "mma_wait_fullA", "mma_wait_tmem", "mma_wait_inter", "mma_total",
+              "gather_wait_emptyA", "-", "epi_wait_full", "epi_up", "epi_silu", "epi_down", "epi_store", "epi_total",
+              "epi_bar", "epi_zero"]
+
+
+def stall_counters(mk, workspace) -> None:
+    """A binary built with -DMONO_PROFILE leaves per-role clock64 sums in the workspace: print their mean over
+    the 148 CTAs, in thousands of cycles, on stderr (the JSON line stays the contract's)."""
+    off = mk._int_symbol("prof_offset")
+    if off is None:
+        return
+    pr = workspace.cpu()[off: off + 148 * 16 * 8].view(torch.int64).view(148, 16).double()
+    if float(pr.sum()) == 0.0:
+        return
+    print("# stall counters of the last launch, mean over CTAs, kcycles: " +
+          ", ".join(f"{n}={pr[:, i].mean().item() / 1e3:.1f}" for i, n in enumerate(PROF_NAMES) if n != "-"),
+          file=sys.stderr)
 
 
 def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barrier, dev, with_logits=True,
