@@ -199,7 +199,7 @@ void prefill_wgmma_set_debug(void* acc, void* inter, void* inter_scale);
  * workspace, the e4m3 activations, routing results, sort permutation and partial rows live in a
  * fixed array inside the library, prefill_wgmma_noalloc_scratch_bytes() per GPU for the life of
  * the process. At most prefill_wgmma_noalloc_max_tokens() tokens (256 for H = 2048, 64 for
- * H = 7168); more returns -130 and launches nothing; -131 if the array's address cannot be
+ * H = 7168, 32 for its shards wider than 512 columns); more returns -130 and launches nothing; -131 if the array's address cannot be
  * resolved. All calls on a device share the array: calls whose kernels overlap on the GPU race,
  * so keep them ordered. The first call on each device looks the array up (cudaGetSymbolAddress);
  * make it outside stream capture. expert_map and router_bias as in the _ep entry (null when unused). */
