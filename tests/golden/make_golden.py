@@ -22,7 +22,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden.py <path of a checkout of the reference repository>")
+REF = sys.argv[1]
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from unimonomoe_b200 import synth  # noqa: E402
 

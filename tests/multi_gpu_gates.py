@@ -39,7 +39,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", default="8192,16384")
     ap.add_argument("--model", default="qwen")
-    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "multi_gpu_gates.json"))
+    ap.add_argument("--out", default=os.path.join(os.environ.get("GATES_OUT_DIR", os.path.join(ROOT, "out")), "multi_gpu_gates.json"))
     args = ap.parse_args()
     dist.init_process_group("nccl")
     rank, world = dist.get_rank(), dist.get_world_size()
