@@ -130,25 +130,25 @@ def test_loader_refuses_unset_binary(monkeypatch):
     loader._reset_prefill_monokernel()
 
 
-def test_validate_mirrors_reference_checks(built_libs):
+def test_validate_checks_every_compiled_dimension(built_libs):
     mk = MonoKernel(built_libs["qwen_tp4"])
     x = torch.zeros(4, 2048, dtype=torch.bfloat16)
     w13 = torch.zeros(256, 256, 2048, dtype=torch.uint8)
     w2 = torch.zeros(256, 2048, 128, dtype=torch.uint8)
     assert mk.validate(x, w13, w2, 8, None) is None
-    with pytest.raises(RuntimeError, match="N_UP=256"):
+    with pytest.raises(RuntimeError, match=r"N_UP\): compiled 256, got 512"):
         mk.validate(x, torch.zeros(256, 512, 2048, dtype=torch.uint8), w2, 8, None)
-    with pytest.raises(RuntimeError, match="N_HALF=128"):
+    with pytest.raises(RuntimeError, match=r"N_HALF\): compiled 128, got 256"):
         mk.validate(x, w13, torch.zeros(256, 2048, 256, dtype=torch.uint8), 8, None)
-    with pytest.raises(RuntimeError, match="K_DIM=2048"):
+    with pytest.raises(RuntimeError, match=r"K_DIM\): compiled 2048, got 1024"):
         mk.validate(torch.zeros(4, 1024, dtype=torch.bfloat16), w13, w2, 8, None)
-    with pytest.raises(RuntimeError, match="local expert slabs"):
+    with pytest.raises(RuntimeError, match=r"E_LOCAL\): compiled 256, got 64"):
         mk.validate(x, w13[:64], w2[:64], 8, None)
-    with pytest.raises(RuntimeError, match="TOP_K=8"):
+    with pytest.raises(RuntimeError, match=r"TOP_K\): compiled 8, got 4"):
         mk.validate(x, w13, w2, 4, None)
     with pytest.raises(RuntimeError, match="softmax"):
         mk.validate(x, w13, w2, 8, torch.zeros(256))
-    with pytest.raises(RuntimeError, match="not EP capable"):
+    with pytest.raises(RuntimeError, match="not an expert-parallel build"):
         mk.validate(x, w13, w2, 8, None, torch.zeros(256, dtype=torch.int32))
     ds = MonoKernel(built_libs["ds_tp8"])
     xd = torch.zeros(4, 7168, dtype=torch.bfloat16)
@@ -157,7 +157,7 @@ def test_validate_mirrors_reference_checks(built_libs):
     ep = MonoKernel(built_libs["qwen_ep4"])
     w13e = torch.zeros(64, 1024, 2048, dtype=torch.uint8)
     w2e = torch.zeros(64, 2048, 512, dtype=torch.uint8)
-    with pytest.raises(RuntimeError, match="no expert_map"):
+    with pytest.raises(RuntimeError, match="no expert_map given"):
         ep.validate(x, w13e, w2e, 8, None)
     with pytest.raises(RuntimeError, match="int32"):
         ep.validate(x, w13e, w2e, 8, None, torch.zeros(256, dtype=torch.int64))

@@ -28,6 +28,33 @@ def test_chunk_table_and_ncomm_overrides(monkeypatch):
     monkeypatch.setenv("VLLM_PREFILL_MONOKERNEL_TP_NCOMM", "0")
     with pytest.raises(ValueError):
         tp_fused.env_ncomm(14)
+    monkeypatch.setenv("VLLM_PREFILL_MONOKERNEL_TP_NCOMM", "20")
+    monkeypatch.setenv("VLLM_PREFILL_MONOKERNEL_TP_CHUNKS", "4096:2,8192:8,16384:8")
+    monkeypatch.setenv("VLLM_PREFILL_MONOKERNEL_TP_FOLD_SHARED", "0")
+    pol = tp_fused.ReducePolicy.from_env(max_tokens=8192)
+    assert dict(pol.chunks_by_tokens) == {4096: 2, 8192: 8} and pol.ncomm == 20 and pol.fold is False
+    assert pol.chunks_for(8192) == 8 and pol.chunks_for(1000) == 0 and pol.max_chunks == 8
+
+
+def test_local_capability_names_the_first_missing_requirement():
+    pol = tp_fused.ReducePolicy()
+    assert tp_fused.probe_capability(None, pol, enabled=False) == (False, False, "the in-kernel reduce is switched off")
+
+    class FakeKernel:
+        def __init__(self, **caps):
+            self.caps = dict(usable=True, tp_has_devseq=1, tp_max_c=16, grid_size=148, has_tp_residual=True)
+            self.caps.update(caps)
+
+        def tp_caps(self):
+            return dict(self.caps)
+
+    if not torch.cuda.is_available():
+        assert "CUDA" in tp_fused.probe_capability(FakeKernel(), pol).why
+        return
+    assert tp_fused.probe_capability(FakeKernel(), pol) == (True, True, "")
+    assert "chunks" in tp_fused.probe_capability(FakeKernel(tp_max_c=4), pol).why
+    assert "launch counter" in tp_fused.probe_capability(FakeKernel(tp_has_devseq=0), pol).why
+    assert tp_fused.probe_capability(FakeKernel(has_tp_residual=False), pol) == (True, False, "")
 
 
 def _free_port():
@@ -46,8 +73,7 @@ def _worker(rank, world, port, answers, q):
         ok, fold = case[rank]
 
         def cap(plan, ok=ok, fold=fold):
-            plan._local_fold = fold
-            return ok, ("" if ok else f"rank {rank} cannot")
+            return tp_fused.Capability(ok, fold, "" if ok else f"rank {rank} cannot")
 
         plan = tp_fused.FusedTPPlan(None, dist.group.WORLD, hidden=2048, max_tokens=16384, capability=cap,
                                     build_pool=False)

@@ -41,6 +41,9 @@ VARIANTS = {
 
 # development variants (not built by default): other epilogue shapes, and the stall-counter build
 DEV_VARIANTS = {
+    "qwen_w1_tanh": dict(QWEN, N_HALF=512, E_LOCAL=256, DEFS=("MONO_SILU_TANH",)),
+    "qwen_w1_st128": dict(QWEN, N_HALF=512, E_LOCAL=256, DEFS=("MONO_ST_LINES",)),
+    "qwen_w1_tanh_st128": dict(QWEN, N_HALF=512, E_LOCAL=256, DEFS=("MONO_SILU_TANH", "MONO_ST_LINES")),
     "qwen_w1_n2": dict(QWEN, N_HALF=512, E_LOCAL=256, EPI_WGS=2, NSPLIT=2),
     "qwen_w1_prof": dict(QWEN, N_HALF=512, E_LOCAL=256, PROFILE=1),
     "qwen_w1_plainst": dict(QWEN, N_HALF=512, E_LOCAL=256, PLAIN_STORES=1),
@@ -79,7 +82,7 @@ def build_variant(variant: str, force: bool = False, verbose: bool = False) -> s
         "-Xptxas", "-v", "-shared", "-Xcompiler", "-fPIC",
         f"-DMONO_K_DIM={g['K']}", f"-DMONO_H_DIM={g['H']}", f"-DMONO_N_HALF={g['N_HALF']}",
         f"-DMONO_E_LOCAL={g['E_LOCAL']}", f"-DMONO_ROUTER_MODE={g['MODE']}", f"-DMONO_EPI_WGS={g.get('EPI_WGS', 2)}", f"-DMONO_NSPLIT={g.get('NSPLIT', 1)}",
-        *(["-DMONO_PROFILE"] if g.get("PROFILE") else []), *(["-DMONO_PLAIN_STORES"] if g.get("PLAIN_STORES") else []), *(["-DMONO_ST_ROWWISE"] if g.get("ST_ROWWISE") else []), *(["-DMONO_GATHER_ROWWISE"] if g.get("GATHER_ROWWISE") else []), f"-DMONO_ABLATE={g.get('ABLATE', 0)}", f"-DMONO_PAIR={g.get('PAIR', 0)}",
+        *(["-DMONO_PROFILE"] if g.get("PROFILE") else []), *(["-DMONO_PLAIN_STORES"] if g.get("PLAIN_STORES") else []), *(["-DMONO_ST_ROWWISE"] if g.get("ST_ROWWISE") else []), *(["-DMONO_GATHER_ROWWISE"] if g.get("GATHER_ROWWISE") else []), f"-DMONO_ABLATE={g.get('ABLATE', 0)}", f"-DMONO_PAIR={g.get('PAIR', 0)}", *[f"-D{d}" for d in g.get("DEFS", ())],
         os.path.join(CSRC, "mono_kernel.cu"), "-o", out,
     ]
     r = subprocess.run(cmd, capture_output=True, text=True)

@@ -838,6 +838,9 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
 
   alive = grid_sync(wc, 1, &S.flag) && alive;
   if (bid == 0 && tid == 0) ws->phase_ns[2] = globaltimer_ns();
+  // phase 1 wrote the operand rings with ordinary stores (histograms, scan arrays); phase 2 fills them through
+  // the async proxy (TMA), so order the two proxies once here
+  fence_proxy_async_smem();
 
   // ================================================================ phase 2
   // Pair build: the MMA thread lives in the cluster's rank-0 CTA ("leader"). Its fullA barrier also
@@ -984,6 +987,8 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             { PROF_T0();
             if (!mbar_wait(&S.fullA[sa], (na / SA) & 1u, wc, kSiteFullA)) { ok = false; break; }
             PROF_ADD(pm_fullA); }
+            // the gathered rows were written by cp.async (generic proxy); the tensor core reads them through the async proxy
+            fence_proxy_async_smem();
             const uint64_t da = umma_desc_sw128(a_ring_u32 + sa * A_STAGE_BYTES);
 #pragma unroll
             for (int j = 0; j < NSPLIT; ++j) {
@@ -1310,8 +1315,16 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
 #pragma unroll
             for (int i = 0; i < HCB / 2; ++i) {
               const float2 g = acc[j * (WC / 2) + i], u = acc[j * (WC / 2) + HCB / 2 + i];
+#ifdef MONO_SILU_TANH
+              // SiLU(g) * u = (u * g/2) * (1 + tanh(g/2)): one special-function operation per element instead of two
+              const float hx = 0.5f * g.x, hy = 0.5f * g.y;
+              const float px = u.x * hx, py = u.y * hy;
+              const float v0 = fmaf(px, tanh_approx(hx), px);
+              const float v1 = fmaf(py, tanh_approx(hy), py);
+#else
               const float v0 = __fdividef(u.x * g.x, 1.0f + __expf(-g.x));
               const float v1 = __fdividef(u.y * g.y, 1.0f + __expf(-g.y));
+#endif
               acc[j * (WC / 2) + i] = make_float2(v0, v1);
               mx = fmaxf(mx, fmaxf(fabsf(v0), fabsf(v1)));
             }

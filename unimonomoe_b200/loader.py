@@ -149,51 +149,47 @@ class MonoKernel:
     # ------------------------------------------------------------------ validation
     def validate(self, activations_in, expert_weights_up, expert_weights_down, top_k, e_score_correction_bias,
                  expert_map=None):
-        """Check this binary against these weights and return the bias to use
-        (_custom_ops.py:4461-4565). Raises RuntimeError on any mismatch."""
+        """Compare the compiled geometry of this binary with the tensors of a call and return the router
+        bias to pass (fp32, contiguous) or None. Any disagreement raises RuntimeError before anything is
+        launched: a binary run on weights of another shape would index out of its tiles. A dimension the
+        binary does not export (None) is not checked. Plays the role of _custom_ops.py:4461-4565."""
         geo = self.geometry()
-        w13_n, w2_n = expert_weights_up.size(1), expert_weights_down.size(2)
-        if geo["n_up"] is not None and geo["n_up"] != w13_n:
-            raise RuntimeError(f"monokernel built for N_UP={geo['n_up']} but w13 has {w13_n}")
-        if geo["n_half"] is not None and geo["n_half"] != w2_n:
-            raise RuntimeError(f"monokernel built for N_HALF={geo['n_half']} but w2 has {w2_n}")
-        if geo["k_dim"] not in (None, activations_in.size(1)):
-            raise RuntimeError(f"monokernel built for K_DIM={geo['k_dim']} but activations have "
-                               f"{activations_in.size(1)}")
-        if geo["h_dim"] not in (None, expert_weights_down.size(1)):
-            raise RuntimeError(f"monokernel built for H_DIM={geo['h_dim']} but w2 has {expert_weights_down.size(1)} rows")
-        n_e = geo["num_experts"]
-        n_local = geo["num_experts_local"] if geo["num_experts_local"] is not None else n_e
-        n_got = expert_weights_up.size(0)
-        if n_local is not None and n_local != n_got:
-            raise RuntimeError(f"monokernel built to index {n_local} local expert slabs but got {n_got}")
+        experts_got = int(expert_weights_up.size(0))
+        local = geo["num_experts_local"] if geo["num_experts_local"] is not None else geo["num_experts"]
+        # (what, compiled value, value of this call)
+        dims = [
+            ("up-projection rows 2*I (N_UP)", geo["n_up"], int(expert_weights_up.size(1))),
+            ("intermediate width I (N_HALF)", geo["n_half"], int(expert_weights_down.size(2))),
+            ("hidden size of the activations (K_DIM)", geo["k_dim"], int(activations_in.size(1))),
+            ("output width (H_DIM)", geo["h_dim"], int(expert_weights_down.size(1))),
+            ("experts whose weights are passed (E_LOCAL)", local, experts_got),
+            ("experts per token (TOP_K)", geo["top_k"], int(top_k)),
+        ]
         if expert_map is None:
-            if n_e is not None and n_e != n_got:
-                raise RuntimeError(f"monokernel built for E={n_e} but got {n_got} experts and no expert_map "
-                                   "to remap them")
+            dims.append(("experts the router scores (E), no expert_map given", geo["num_experts"], experts_got))
         else:
             if not geo["ep_capable"]:
-                raise RuntimeError("an expert_map was supplied but the loaded monokernel .so is not EP capable; "
-                                   "its weight indexing would use global expert ids")
+                raise RuntimeError("expert_map given, but this binary is not an expert-parallel build: it would "
+                                   "index the weights with global expert ids")
             if expert_map.dtype != torch.int32:
-                raise RuntimeError(f"expert_map must be int32, got {expert_map.dtype}")
-            if n_e is not None and expert_map.numel() != n_e:
-                raise RuntimeError(f"monokernel built for E={n_e} but expert_map has {expert_map.numel()} entries")
-        if geo["top_k"] not in (None, int(top_k)):
-            raise RuntimeError(f"monokernel built for TOP_K={geo['top_k']} but got top_k={top_k}")
-        bias = e_score_correction_bias
-        if bias is not None:
-            if geo["router_mode"] == 0:
-                raise RuntimeError("monokernel .so is a softmax (ROUTER_MODE 0) build and cannot apply an "
+                raise RuntimeError(f"expert_map has dtype {expert_map.dtype}; the kernel reads int32")
+            dims.append(("entries of expert_map (E)", geo["num_experts"], int(expert_map.numel())))
+        wrong = [f"{what}: compiled {want}, got {got}" for what, want, got in dims if want is not None and want != got]
+        if wrong:
+            raise RuntimeError(f"{os.path.basename(self.path)} does not fit this call: " + "; ".join(wrong))
+
+        mode = geo["router_mode"]
+        if e_score_correction_bias is None:
+            if mode not in (None, 0):
+                raise RuntimeError(f"this binary routes with sigmoid + bias (ROUTER_MODE {mode}) and needs an "
                                    "e_score_correction_bias")
-            if not self.has_router:
-                raise RuntimeError("monokernel .so does not export launch_prefill_moe_wgmma_q1_router, so a "
-                                   "correction bias cannot be passed")
-            return bias.float().contiguous()
-        if geo["router_mode"] not in (None, 0):
-            raise RuntimeError(f"monokernel .so is a ROUTER_MODE {geo['router_mode']} (sigmoid) build but no "
-                               "e_score_correction_bias was supplied")
-        return None
+            return None
+        if mode == 0:
+            raise RuntimeError("this binary routes with softmax (ROUTER_MODE 0) and has no use for an "
+                               "e_score_correction_bias")
+        if not self.has_router:
+            raise RuntimeError("this binary lacks launch_prefill_moe_wgmma_q1_router, the entry that takes the bias")
+        return e_score_correction_bias.float().contiguous()
 
     # ------------------------------------------------------------------ scratch
     def scratch(self, M: int, device) -> dict:
