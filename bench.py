@@ -4,10 +4,14 @@
 
 One step = one pass of the layer (route -> sort -> up/SiLU/requant/down -> reduce) over one
 synthetic prefill batch. N=1 runs the Qwen3.5-35B-A3B-like layer (H=2048, E=256, top-8,
-I=512, block-FP8 weights) at T=16384 tokens; N=2/4 run the same layer tensor-parallel
-(I/N per rank), N=8 expert-parallel (32 experts per rank), output reduced across ranks.
-Prints ONE JSON line (rank 0). --impl reference times the reference's CPU path (torch MoE on
-dequantised weights, host cores) on a bounded sample of the same workload.
+I=512, block-FP8 weights) at T=16384 tokens; N>1 runs the same layer expert-parallel (256/N
+experts per rank, all tokens on every rank) with the ranks' partial outputs reduced inside the
+kernel or by NCCL after it, whichever was measured faster for that N (--reduce overrides;
+--parallel tp selects the tensor-parallel split, --model deepseek the DeepSeek-V3-like layer).
+Before anything is timed at N>1 the reduced output of exactly that configuration is checked
+against an unfused launch + all-reduce and against the CPU oracle. Prints ONE JSON line (rank 0).
+--impl reference times the reference's CPU path (torch MoE on dequantised weights, host cores)
+on a bounded sample of the same workload.
 """
 from __future__ import annotations
 
@@ -126,33 +130,56 @@ def fp8_gemm_tflops(dev) -> float | None:
         return None
 
 
-def cpu_reference_moe(spec, layer_cpu, hs, logits, threads: int, dtype=torch.float32):
-    """The reference's CPU path: softmax top-8 routing on the logits, then per expert
-    x @ W13^T -> SiLU(gate)*up -> @ W2^T on dequantised block-FP8 weights, weighted sum
-    (validation/ep4_acc.py:183-217), in torch on `threads` host threads."""
+REFERENCE_SAMPLE_TOKENS = 2048   # 64 rows per expert on average; a pass stays within seconds on host cores
+
+
+def cpu_reference_layer(spec, layer_cpu, hs, threads: int, dtype=torch.float32, with_router=True, with_shared=True):
+    """The reference's CPU path for one layer, in torch on `threads` host threads: router linear, softmax
+    top-8 with renormalised weights, per expert x @ W13^T -> SiLU(gate)*up -> @ W2^T on dequantised
+    block-FP8 weights and the weighted sum (validation/ep4_acc.py:183-217), plus the sigmoid-gated shared
+    expert. Returns the layer output."""
     from oracle import cpu_oracle as O
     torch.set_num_threads(threads)
+    if with_router:
+        logits = torch.nn.functional.linear(hs.to(dtype), layer_cpu["router_w"].to(dtype)).float()
+    else:
+        logits = layer_cpu["_logits"]
     top = torch.topk(logits, spec.top_k, dim=1)
     w = torch.softmax(logits, 1).gather(1, top.indices)
     w = w / w.sum(1, keepdim=True).clamp(min=1e-30)
-    return O.moe_fp64(hs, top.indices, w, layer_cpu["w13"], layer_cpu["w13_scale"], layer_cpu["w2"],
-                      layer_cpu["w2_scale"], dtype=dtype)
+    out = O.moe_fp64(hs, top.indices, w, layer_cpu["w13"], layer_cpu["w13_scale"], layer_cpu["w2"],
+                     layer_cpu["w2_scale"], dtype=dtype)
+    if with_shared and layer_cpu.get("shared") is not None:
+        out = out + O.shared_expert_fp(hs, layer_cpu["shared"], dtype=dtype)
+    return out
+
+
+def _cpu_case(spec, tokens):
+    layer = synth.make_layer(spec, seed=0, device="cpu", with_shared=True)
+    batch = synth.make_batch(spec, layer, tokens, seed=0, device="cpu")
+    layer["_logits"] = batch["logits"]
+    return layer, batch
+
+
+def _time_cpu(fn, reps: int) -> float:
+    fn()
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times)
 
 
 def time_cpu_baseline(spec, sample_tokens: int, reps: int = 2) -> dict:
     threads = os.cpu_count() or 1
-    layer = synth.make_layer(spec, seed=0, device="cpu", with_shared=False)
-    batch = synth.make_batch(spec, layer, sample_tokens, seed=0, device="cpu")
-    times = []
-    for _ in range(reps + 1):
-        t0 = time.perf_counter()
-        cpu_reference_moe(spec, layer, batch["hs"], batch["logits"], threads)
-        times.append(time.perf_counter() - t0)
-    sec = statistics.median(times[1:])
+    layer, batch = _cpu_case(spec, sample_tokens)
+    sec = _time_cpu(lambda: cpu_reference_layer(spec, layer, batch["hs"], threads), reps)
     fl = synth.routed_flops(spec, sample_tokens)
     return {"value": fl / sec / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"{sample_tokens} tokens of the same layer (all 256 experts), torch fp32 on dequantised "
-                      f"weights, median of {reps} passes, {sec * 1e3:.0f} ms per pass",
+            "sample": f"{sample_tokens} tokens of the same layer (all 256 experts): router linear, softmax top-8, routed "
+                      f"experts and the gated shared expert in torch fp32 on dequantised weights, median of {reps} "
+                      f"passes, {sec * 1e3:.0f} ms per pass; value counts the routed FLOPs only",
             "ms_per_step": sec * 1e3}
 
 
@@ -161,26 +188,36 @@ def run_reference(args) -> None:
     if rank != 0:
         return
     spec = synth.QWEN
-    sample = 256
-    times = []
+    sample = REFERENCE_SAMPLE_TOKENS
     threads = os.cpu_count() or 1
-    layer = synth.make_layer(spec, seed=0, device="cpu", with_shared=False)
-    batch = synth.make_batch(spec, layer, sample, seed=0, device="cpu")
+    layer, batch = _cpu_case(spec, sample)
+    times = []
     for i in range(args.warmup + args.steps):
         t0 = time.perf_counter()
-        cpu_reference_moe(spec, layer, batch["hs"], batch["logits"], threads)
+        cpu_reference_layer(spec, layer, batch["hs"], threads)
         if i >= args.warmup:
             times.append(time.perf_counter() - t0)
     sec = sum(times) / len(times)
-    val = synth.routed_flops(spec, sample) / sec / 1e12
+    # context: the same pass in the oracle's own precision, and the routed experts alone
+    sec64 = _time_cpu(lambda: cpu_reference_layer(spec, layer, batch["hs"], threads, dtype=torch.float64), 1)
+    sec_routed = _time_cpu(lambda: cpu_reference_layer(spec, layer, batch["hs"], threads, with_router=False,
+                                                       with_shared=False), 1)
+    flops = synth.routed_flops(spec, sample)
+    val = flops / sec / 1e12
+    what = (f"{spec.name} MoE layer, reference CPU path (router linear, softmax top-8, routed experts on dequantised "
+            f"block-FP8 weights, gated shared expert; torch fp32, {threads} host threads) on a {sample}-token batch "
+            f"(the GPU arm runs T={args.tokens})")
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{spec.name} MoE layer, reference CPU path on a {sample}-token sample of the "
-                               f"T={args.tokens} batch", "tokens": args.tokens, "sample_tokens": sample},
+        "config": {"workload": what, "tokens": sample, "gpu_arm_tokens": args.tokens},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{sample} tokens per step, torch fp32 dequantised MoE (validation/ep4_acc.py:183-217 restated)"},
+                         "sample": f"{sample} tokens per step: {what}; value counts the routed FLOPs only",
+                         "fp64_ms_per_step": sec64 * 1e3, "fp64_value": flops / sec64 / 1e12,
+                         "routed_experts_only_ms_per_step": sec_routed * 1e3,
+                         "flops_incl_router_and_shared": flops + 2.0 * sample * spec.hidden * spec.experts
+                         + 6.0 * sample * spec.hidden * spec.shared_inter},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -199,7 +236,14 @@ def main() -> None:
                     help="deepseek: DeepSeek-V3-like layer (H=7168, I=2048, grouped sigmoid router), tensor parallel, N=4 or 8")
     ap.add_argument("--parallel", default="auto", choices=["auto", "tp", "ep"],
                     help="N>1: tensor parallel (N=2,4) or expert parallel; auto = ep")
-    ap.add_argument("--unfused", action="store_true", help="N>1: reduce with NCCL after the kernel instead of in-kernel")
+    ap.add_argument("--unfused", action="store_true", help="N>1: same as --reduce nccl")
+    ap.add_argument("--reduce", default="auto", choices=["auto", "fused", "nccl"],
+                    help="N>1: all-reduce of the ranks' partial outputs inside the kernel (NVLS multimem) or by NCCL "
+                         "after it; auto takes what FUSED_REDUCE_WINS records as faster for this split and N")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0,
+                    help="after the timed steps, repeat the same launch for this long and report the steady-state "
+                         "time and clocks (0: skip)")
+    ap.add_argument("--no-verify", action="store_true", help="N>1: skip the pre-timing parity check (profiling runs)")
     ap.add_argument("--router", default="logits", choices=["logits", "gemv"],
                     help="logits: the caller's router logits go in (the reference's interface); gemv: the bf16 gate "
                          "weight goes in and the router linear runs inside the launch (no logits cross PCIe in e2e)")
@@ -261,7 +305,11 @@ def main() -> None:
     plan = None
     # 32 communication CTAs measured best on B200 (14, 32 and 48 tried at four ranks)
     os.environ.setdefault("VLLM_PREFILL_MONOKERNEL_TP_NCOMM", "32")
-    if world > 1 and not args.unfused:
+    reduce_mode = "nccl" if args.unfused else args.reduce
+    if reduce_mode == "auto":
+        reduce_mode = "fused" if FUSED_REDUCE_WINS.get((args.model, par[:2], world), True) else "nccl"
+    if world > 1:
+        # the symmetric pool is built even when NCCL reduces: the parity check before the timing uses it
         plan = tp_fused.FusedTPPlan(mk, dist.group.WORLD, hidden=spec.hidden, max_tokens=T, nslots=2)
         if plan.usable and plan.chunks_for(T) == 0:
             plan.chunks_by_tokens[T] = 8 if T >= 16384 else 4
@@ -269,6 +317,9 @@ def main() -> None:
             if rank == 0:
                 print(f"# fused TP epilogue unavailable ({plan.reason}); reducing with NCCL", file=sys.stderr)
             plan = None
+    pool_plan = plan                      # kept for the parity check
+    if reduce_mode != "fused":
+        plan = None
     reduce_desc = "none" if world == 1 else (
         f"in-kernel NVLS multimem all-reduce, {plan.chunks_for(T)} chunks, {plan.ncomm} communication CTAs"
         if plan is not None else "NCCL all-reduce after the kernel")
@@ -306,6 +357,16 @@ def main() -> None:
     barrier()
     mk.check_status(sc["workspace"])
 
+    parity = None
+    if world > 1 and not args.no_verify:
+        result_now = plan.pool.output(T) if plan is not None else out
+        parity = verify_reduced_output(spec, mk, layer, batch, emap, sc, pool_plan, result_now, world, rank, dist, dev,
+                                       par, kw, fused=plan is not None)
+        if not parity["ok"]:
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "parity_checked": False, "parity": parity}), flush=True)
+            raise SystemExit(3)
+
     # ---- device-resident timing: K steps between two events, plus one event pair per kernel launch
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -330,6 +391,12 @@ def main() -> None:
     flops = synth.routed_flops(spec, T)  # whole job: all ranks together
     value = flops / (ms_per_step * 1e-3) / 1e12
 
+    sustained = None
+    if args.sustained_seconds > 0:
+        sustained = run_sustained(args.sustained_seconds, ms_per_step, launch, reduce_out, batch, barrier, world, dist, dev,
+                                  physical_gpu_index(local), flops)
+        mk.check_status(sc["workspace"])
+
     e2e_ms = None
     if not args.kernel_only:
         result = plan.pool.output(T) if plan is not None else out
@@ -346,7 +413,7 @@ def main() -> None:
         phases = [round((ph[i + 1] - ph[i]) / 1e3, 1) for i in range(4)]
         stall_counters(mk, sc["workspace"])
         report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
-               reduce_desc, phases)
+               reduce_desc, phases, sustained, parity)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -512,8 +579,104 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barr
     return piped_ms, serial_ms, gather_ms, gather_kind
 
 
+# (model, split, ranks) -> is the reduce inside the kernel faster than NCCL after it? Measured on B200 at
+# T=16384; a split that is not listed takes the in-kernel reduce.
+FUSED_REDUCE_WINS = {("qwen", "ep", 2): False, ("qwen", "ep", 4): False, ("qwen", "ep", 8): True}
+
+
+def run_sustained(seconds, ms_guess, launch, reduce_out, batch, barrier, world, dist, dev, gpu_index, flops) -> dict:
+    """The same launch repeated for `seconds`: the steady-state figure under the power cap, with the clocks
+    seen. Nothing here touches a clock; time x median SM MHz is the clock-normalised cost."""
+    n = max(20, int(seconds * 1e3 / max(ms_guess, 1e-3)))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(gpu_index) as clk:
+        barrier()
+        e0.record()
+        for _ in range(n):
+            launch(batch["hs"], batch["logits"])
+            reduce_out()
+        e1.record()
+        barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / n], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    c = clk.summary()
+    return {"steps": n, "ms_per_step": ms, "value": flops / (ms * 1e-3) / 1e12, "sm_mhz_median": c["sm_mhz"],
+            "reasons": c["reasons"], "clock_samples": c["samples"],
+            "us_times_ghz": (ms * 1e3 * c["sm_mhz"] / 1e3) if c["sm_mhz"] else None}
+
+
+def _bf16_order_key(t):
+    b = t.contiguous().view(torch.int16).to(torch.int32) & 0xFFFF
+    return torch.where(b >= 0x8000, 0x8000 - b, b)
+
+
+def verify_reduced_output(spec, mk, layer, batch, emap, sc, pool_plan, result, world, rank, dist, dev, par, shard_kw,
+                          fused) -> dict:
+    """Before anything is timed on N > 1 GPUs: the reduced output of the configuration that is about to be
+    timed (`result`, left there by the warm-up steps) must
+      * when the reduce ran inside the kernel: equal an ordinary launch followed by torch's multimem
+        all-reduce bit for bit (both sum in fp32 inside the switch and round once),
+      * agree with an ordinary launch + NCCL all-reduce (ulp statistics reported, the largest difference
+        bounded against the output's rms: NCCL may sum in another order and round between hops),
+      * match the CPU oracle on sampled tokens within the layer's tolerance (rank 0 evaluates every rank's shard).
+    Every rank returns the same verdict."""
+    T, H = batch["hs"].shape[0], spec.hidden
+    got = result.clone()
+    info = {}
+    plain = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    mk.prefill_impl(batch["hs"], batch["logits"], layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"],
+                    spec.top_k, True, layer["bias"], plain, expert_map=emap, scratch=sc, check=True)
+    ok = True
+    if pool_plan is not None:
+        view = pool_plan.pool.output(T, 1)
+        view.copy_(plain)
+        torch.ops.symm_mem.multimem_all_reduce_(view, "sum", dist.group.WORLD.group_name)
+        torch.cuda.synchronize()
+        info["bitwise_equal_to_kernel_plus_multimem_all_reduce"] = bool(
+            torch.equal(got.view(torch.int16), view.view(torch.int16)))
+        if fused:
+            ok = ok and info["bitwise_equal_to_kernel_plus_multimem_all_reduce"]
+    dist.all_reduce(plain)
+    d = (_bf16_order_key(got) - _bf16_order_key(plain)).abs()
+    rms = float(plain.float().pow(2).mean().sqrt())
+    max_abs = float((got.float() - plain.float()).abs().max())
+    info["vs_kernel_plus_nccl"] = {"moved": int((d > 0).sum()), "over_1_ulp": int((d > 1).sum()), "max_ulp": int(d.max()),
+                                   "max_abs_over_rms": max_abs / max(rms, 1e-30)}
+    ok = ok and max_abs <= 2e-2 * rms
+    if rank == 0:
+        import numpy as np
+        from oracle import cpu_oracle as O
+        n_tok = 64 if H <= 2048 else 8
+        toks = np.sort(np.random.RandomState(7).choice(T, n_tok, replace=False)).astype(np.int32)
+        ids, w, _ = O.route(batch["logits"], mode=spec.router_mode, bias=layer["bias"])
+        q, s = O.quant_act(batch["hs"])
+        tot = torch.zeros(n_tok, H)
+        n_e = spec.experts // world
+        for rr in range(world):
+            if par.startswith("ep"):
+                kw_r = {"expert_slice": (rr * n_e, (rr + 1) * n_e)}
+                ids_r = np.where((ids >= rr * n_e) & (ids < (rr + 1) * n_e), ids - rr * n_e, -1).astype(np.int32)
+            else:
+                n_i = spec.inter // world
+                kw_r = {"inter_slice": (rr * n_i, (rr + 1) * n_i)}
+                ids_r = ids
+            sh = layer if rr == rank else synth.make_layer(spec, seed=0, device=dev, with_shared=False,
+                                                           chunk=shard_kw.get("chunk", 16), **kw_r)
+            tot += O.moe_path(toks, q, s, ids_r, w, sh["w13"], sh["w13_scale"], sh["w2"], sh["w2_scale"]).float()
+            del sh
+        m = O.parity_metrics(got.float().cpu()[torch.from_numpy(toks).long()], tot)
+        info["oracle"] = {"tokens": n_tok, **m}
+        ok = ok and m["max_abs_over_rms"] <= 2e-2 and m["cos"] >= 0.9995
+    flag = torch.tensor([1.0 if ok else 0.0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    info["ok"] = bool(flag.item() == 1.0)
+    return info
+
+
 def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
-           reduce_desc, phases=None) -> None:
+           reduce_desc, phases=None, sustained=None, parity=None) -> None:
     peaks = measured_peaks()
     fp8_lib = fp8_gemm_tflops(dev) if (world == 1 and not args.kernel_only) else None
     if peaks.get("bf16_tflops"):
@@ -558,8 +721,16 @@ def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flop
                      "traffic": traffic, "peak_source": peak_src, "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
                      "library_fp8_gemm_tflops": fp8_lib},
     }
+    if sustained is not None:
+        sus_peak = 2.0 * float(peaks.get("bf16_tflops_sustained") or 1400.0)
+        sustained["frac_of_2x_bf16_sustained"] = (flops / world) / (sustained["ms_per_step"] * 1e-3) / 1e12 / sus_peak
+        sustained["peak_2x_bf16_sustained"] = sus_peak
+        line["sustained"] = sustained
+    if world > 1:
+        line["parity_checked"] = bool(parity is not None and parity["ok"])
+        line["parity"] = parity
     if world == 1 and not args.no_cpu_baseline and not args.kernel_only:
-        line["cpu_baseline"] = time_cpu_baseline(spec, 256)
+        line["cpu_baseline"] = time_cpu_baseline(spec, REFERENCE_SAMPLE_TOKENS)
     print(json.dumps(line), flush=True)
 
 

@@ -213,3 +213,23 @@ def test_token_cap_is_enforced_before_any_cuda_call(built_libs, monkeypatch):
     x = torch.empty(30721, 2048, dtype=torch.bfloat16).as_subclass(FakeCuda)
     with pytest.raises(RuntimeError, match="refuses 30721 tokens"):
         mk.prefill_impl(x, None, None, None, torch.empty(256, 2048, 512), None, 8, True, None, None)
+
+
+def test_scratch_arena_grows_and_never_frees(built_libs):
+    """The scratch of a launch comes from one grow-only arena per device: smaller batches are views of it, a
+    larger batch adds a larger arena, and the outgrown one stays alive (a captured graph may hold its addresses)."""
+    mk = MonoKernel(built_libs["qwen_tp4"])
+    a = mk.scratch(100, "cpu")
+    b = mk.scratch(50, "cpu")
+    assert a["workspace"].data_ptr() == b["workspace"].data_ptr()
+    assert a["act_fp8"].data_ptr() == b["act_fp8"].data_ptr() and b["act_fp8"].shape == (50, 2048)
+    assert b["partial"].shape == (50 * 8, 2048) and b["sorted_ids"].shape == (400,)
+    assert mk.scratch(50, "cpu") is b                      # the views of a size are made once
+    old_ptr = a["partial"].data_ptr()
+    for m in (60, 70, 80, 90, 100, 30):                    # more sizes than any small cache would hold
+        assert mk.scratch(m, "cpu")["partial"].data_ptr() == old_ptr
+    c = mk.scratch(200, "cpu")
+    assert c["partial"].data_ptr() != old_ptr and c["partial"].shape == (1600, 2048)
+    assert len(mk._retired) == 1 and mk._retired[0]["buffers"]["partial"].data_ptr() == old_ptr
+    assert mk.scratch(100, "cpu")["partial"].data_ptr() == c["partial"].data_ptr()   # later calls use the larger arena
+    assert a["partial"].data_ptr() == old_ptr              # what was handed out earlier is still the same memory

@@ -42,6 +42,10 @@ VARIANTS = {
 # development variants (not built by default): other epilogue shapes, and the stall-counter build
 DEV_VARIANTS = {
     "qwen_w1_tanh": dict(QWEN, N_HALF=512, E_LOCAL=256, DEFS=("MONO_SILU_TANH",)),
+    **{f"qwen_w1_pf{d}": dict(QWEN, N_HALF=512, E_LOCAL=256, DEFS=(f"MONO_PF_DIST={d}",)) for d in (4, 8, 16, 32)},
+    **{f"qwen_w1_tanh_pf{d}": dict(QWEN, N_HALF=512, E_LOCAL=256, DEFS=("MONO_SILU_TANH", f"MONO_PF_DIST={d}")) for d in (8, 16)},
+    "qwen_w1_tanh_pf8_e4": dict(QWEN, N_HALF=512, E_LOCAL=256, EPI_WGS=4, DEFS=("MONO_SILU_TANH", "MONO_PF_DIST=8")),
+    "qwen_w1_tanh_pf8_prof": dict(QWEN, N_HALF=512, E_LOCAL=256, PROFILE=1, DEFS=("MONO_SILU_TANH", "MONO_PF_DIST=8")),
     "qwen_w1_st128": dict(QWEN, N_HALF=512, E_LOCAL=256, DEFS=("MONO_ST_LINES",)),
     "qwen_w1_tanh_st128": dict(QWEN, N_HALF=512, E_LOCAL=256, DEFS=("MONO_SILU_TANH", "MONO_ST_LINES")),
     "qwen_w1_n2": dict(QWEN, N_HALF=512, E_LOCAL=256, EPI_WGS=2, NSPLIT=2),

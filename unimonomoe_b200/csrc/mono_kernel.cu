@@ -106,6 +106,7 @@ constexpr int CHUNK_COLS = N_HALF > 512 ? 512 : N_HALF;
 constexpr int NCH = N_HALF / CHUNK_COLS;
 constexpr int NP = CHUNK_COLS / 128;  // 128-column passes of the up projection = K slabs of the down projection, per chunk
 static_assert(N_HALF % CHUNK_COLS == 0, "the intermediate splits into whole chunks");
+static_assert(CHUNK_COLS / 128 <= 4, "one intermediate-ready barrier per pass: at most four passes");
 constexpr int NHB = H_DIM / 256;   // 256-column passes of the down projection
 constexpr int TILE_M = 128;
 
@@ -128,6 +129,10 @@ static_assert(ROUTER_MODE != 2 || N_GROUP * 32 == E, "grouped routing assumes 32
 #ifndef MONO_NSPLIT
 #define MONO_NSPLIT 1
 #endif
+// Weight slabs requested into L2 ahead of the shared-memory loads (0: no prefetch).
+#ifndef MONO_PF_DIST
+#define MONO_PF_DIST 0
+#endif
 // MONO_PAIR=1: tiles are scheduled as pairs of 128-row tiles of one expert on a cluster of two CTAs
 // (tcgen05 cta_group::2, M = 256). Each CTA gathers its own 128 activation rows and loads HALF of every
 // weight stage; one thread of the cluster's rank-0 CTA issues the MMAs for both. Halves the weight
@@ -137,6 +142,7 @@ static_assert(ROUTER_MODE != 2 || N_GROUP * 32 == E, "grouped routing assumes 32
 #endif
 constexpr bool PAIR = MONO_PAIR != 0;
 constexpr int EPI_WGS = MONO_EPI_WGS;
+constexpr int PF_DIST = MONO_PF_DIST;
 static_assert(EPI_WGS == 2 || EPI_WGS == 4, "two or four epilogue warpgroups");
 static_assert(!PAIR || (EPI_WGS == 2 && MONO_NSPLIT == 1), "the pair schedule is written for two epilogue warpgroups, N = 256");
 // A 128-deep K slab of the 256 weight rows of a stage is issued as NSPLIT independent MMAs of
@@ -509,7 +515,7 @@ __device__ __forceinline__ size_t wsd_index(int e, int chunk, int i) {
 struct __align__(16) SharedState {
   uint64_t fullA[STAGE_CAP], emptyA[STAGE_CAP], fullB[STAGE_CAP], emptyB[STAGE_CAP];
   uint64_t tmem_full[NBUF], tmem_empty[NBUF];
-  uint64_t inter_ready;
+  uint64_t inter_ready[4];  // one per 128-column pass of the intermediate (NP <= 4)
   uint64_t rfull[4], rempty[4], racc_full, racc_empty;  // phase R only
   uint32_t tmem_base;
   uint32_t flag;          // grid_sync result broadcast
@@ -856,7 +862,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
     }
     for (int s = 0; s < SB; ++s) { mbar_init(&S.fullB[s], 1); mbar_init(&S.emptyB[s], 1); }
     for (int s = 0; s < NBUF; ++s) { mbar_init(&S.tmem_full[s], 1); mbar_init(&S.tmem_empty[s], both * (N_EPI / 32)); }
-    mbar_init(&S.inter_ready, both * (N_EPI / 32));
+    for (int s = 0; s < NP; ++s) mbar_init(&S.inter_ready[s], both * (N_EPI / 32));
     mbar_init_fence();
   }
   if (warp == WARP_MMA && !gemv) {  // phase R already holds the allocation
@@ -889,6 +895,33 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         uint32_t nb = 0;
         bool ok = true;
         PROF_DECL(pw_emptyB);
+        // A second cursor walks the same sequence of weight slabs PF_DIST slabs ahead of the loads and asks
+        // for them to be brought into L2: the operand ring holds only three slabs, too few to cover the
+        // latency of HBM, which every expert's weights come from the first time they are touched.
+        int pf_it = 0, pf_s = 0;
+        auto prefetch_next = [&]() {
+          if constexpr (PF_DIST > 0 && !PAIR) {
+            if (pf_it >= n_my) return;
+            const int e = S.tiles[pf_it].e, ch = S.tiles[pf_it].chunk;
+            if (pf_s < NP * NK) {
+              const int ps = pf_s / NK, ks = pf_s % NK;
+              const uint32_t yg = static_cast<uint32_t>(e * N_UP + ch * CHUNK_COLS + ps * 128);
+#pragma unroll
+              for (int c = 0; c < 128; c += HCB) {
+                tma_prefetch_l2_2d(&p.tm_up, static_cast<uint32_t>(ks * 128), yg + c);
+                tma_prefetch_l2_2d(&p.tm_up, static_cast<uint32_t>(ks * 128), yg + N_HALF + c);
+              }
+            } else {
+              const int sd = pf_s - NP * NK, hb = sd / NP, dk = sd % NP;
+              const uint32_t y = static_cast<uint32_t>(e * H_DIM + hb * 256);
+#pragma unroll
+              for (int j = 0; j < 256 / HCB; ++j)
+                tma_prefetch_l2_2d(&p.tm_down, static_cast<uint32_t>((ch * NP + dk) * 128), y + j * HCB);
+            }
+            if (++pf_s == NP * NK + NHB * NP) { pf_s = 0; ++pf_it; }
+          }
+        };
+        for (int i = 0; i < PF_DIST; ++i) prefetch_next();
         for (int it = 0; it < n_my && ok; ++it) {
           const int e = S.tiles[it].e, ch = S.tiles[it].chunk;
           for (int ps = 0; ps < NP && ok; ++ps) {
@@ -925,6 +958,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
                   tma_load_2d(&p.tm_up, x, yu + co, dst + (j * BC + hh * WC + HCB) * 128, &S.fullB[st]);
                 }
               }
+              prefetch_next();
               ++nb;
             }
           }
@@ -947,6 +981,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               if constexpr ((MONO_ABLATE & 16) != 0) { ++nb; continue; }
 #pragma unroll
               for (int j = 0; j < 256 / HCB; ++j) tma_load_2d(&p.tm_down, x, y + j * HCB, dst + j * HCB * 128, &S.fullB[st]);
+              prefetch_next();
               ++nb;
             }
           }
@@ -1016,13 +1051,17 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             ++nb; ++na;
           }
           if (!ok) break;
-          { PROF_T0();
-          if (!mbar_wait(&S.inter_ready, static_cast<uint32_t>(it) & 1u, wc, kSiteInterReady)) { ok = false; break; }
-          PROF_ADD(pm_inter); }
-          tc_fence_after();
           for (int s = 0; s < NHB * NP; ++s) {
             const int dk = s % NP;
             const uint32_t sb = nb % SB;
+            if (s < NP) {
+              // K slab dk of the down projection reads the 128 intermediate columns pass dk wrote: the first
+              // slabs start while the epilogue is still in the SiLU section of the last pass
+              { PROF_T0();
+              if (!mbar_wait(&S.inter_ready[dk], static_cast<uint32_t>(it) & 1u, wc, kSiteInterReady)) { ok = false; break; }
+              PROF_ADD(pm_inter); }
+              tc_fence_after();
+            }
             { PROF_T0();
             if (!mbar_wait(&S.fullB[sb], (nb / SB) & 1u, wc, kSiteFullB)) { ok = false; break; }
             PROF_ADD(pm_fullB); }
@@ -1359,12 +1398,12 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
           }
           if (p.dbg_inter_scale != nullptr && fi >= 0 && h == 0 && !dead)
             p.dbg_inter_scale[static_cast<size_t>(ti.row0 + r) * NPT + ti.chunk * NP + ps] = my_scale;
+          // publish this pass's 128 intermediate columns to the tensor core (async proxy)
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) { if (PAIR && !leader) mbar_arrive_cluster(at_leader(&S.inter_ready[ps])); else mbar_arrive(&S.inter_ready[ps]); }
           PROF_ADD(pe_silu);
         }
-        // publish the intermediate to the tensor core (async proxy) and release the MMA thread
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) { if (PAIR && !leader) mbar_arrive_cluster(at_leader(&S.inter_ready)); else mbar_arrive(&S.inter_ready); }
 
         // ---------------- down projection, routing weight, bf16 partial rows.
         // Every epilogue thread is past the last pass's barrier, so nobody reads this tile's

@@ -82,6 +82,13 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap* m, uint32_t x, ui
       : "memory");
 }
 
+// The same tile brought into L2 only (no shared-memory destination, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, uint32_t x, uint32_t y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y)
+               : "memory");
+}
+
 // ---------------------------------------------------------------- cp.async (16 B, L2 only)
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");

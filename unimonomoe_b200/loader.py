@@ -8,8 +8,8 @@ module in behind ``Fp8MoEMethod.try_moe_monokernel``. Differences, all deliberat
 * several binaries can be loaded in one process (one ``MonoKernel`` per .so); the
   module-level functions act on the binary named by ``VLLM_PREFILL_MONOKERNEL_SO`` exactly
   as the reference does, and refuse to guess when it is unset (_custom_ops.py:4259-4272);
-* scratch buffers are cached per (device, tokens) instead of being allocated on every call
-  (_custom_ops.py:4645-4652), and the per-slot partial buffer is bf16, the size the kernel
+* scratch buffers come from one grow-only arena per device instead of being allocated on every
+  call (_custom_ops.py:4645-4652), and the per-slot partial buffer is bf16, the size the kernel
   really touches;
 * every device-side wait of the kernel is bounded; ``check_status`` reads the status word.
 
@@ -89,7 +89,8 @@ class MonoKernel:
         except AttributeError:
             self._pad_words_fn = None
         self._geo = None
-        self._scratch = {}
+        self._scratch = {}    # device -> arena
+        self._retired = []    # outgrown arenas, kept alive for captured graphs
         try:
             lib.prefill_wgmma_set_wait_timeout_us.argtypes = [ctypes.c_ulonglong]
             lib.prefill_wgmma_set_wait_timeout_us.restype = None
@@ -192,25 +193,51 @@ class MonoKernel:
         return e_score_correction_bias.float().contiguous()
 
     # ------------------------------------------------------------------ scratch
-    def scratch(self, M: int, device) -> dict:
-        """Caller-owned scratch for M tokens on device, created once and reused."""
+    def _allocate_scratch(self, tokens: int, device) -> dict:
         geo = self.geometry()
-        key = (str(device), int(M))
-        sc = self._scratch.get(key)
+        K, H, k = geo["k_dim"], geo["h_dim"], geo["top_k"]
+        chunks = self._int_symbol("partial_chunks") or 1
+        return {
+            "workspace": torch.zeros(geo["workspace_bytes"], dtype=torch.uint8, device=device),
+            "act_fp8": torch.empty(tokens, K, dtype=torch.uint8, device=device),
+            "act_scales": torch.empty(tokens, K // 128, dtype=torch.float32, device=device),
+            "topk_ids": torch.empty(tokens, k, dtype=torch.int32, device=device),
+            "topk_weights": torch.empty(tokens, k, dtype=torch.float32, device=device),
+            "sorted_ids": torch.empty(tokens * k, dtype=torch.int32, device=device),
+            "partial": torch.empty(tokens * k * chunks, H, dtype=torch.bfloat16, device=device),
+        }
+
+    def scratch(self, M: int, device) -> dict:
+        """The scratch buffers of a launch for M tokens on `device` (the reference allocates them on
+        every call, _custom_ops.py:4645-4652).
+
+        One arena per device, sized for the largest batch seen so far; a call for fewer tokens gets
+        views of its first rows, so a new prefill length costs no allocation. Nothing is ever handed back
+        to the allocator while this object lives: when a larger batch arrives a larger arena is added
+        and the old one is kept, because a captured CUDA graph may still hold its addresses. While the
+        current stream is capturing, a batch that does not fit gets fresh buffers that are not cached, so
+        that the capture's own memory pool owns them. All launches through one MonoKernel share the arena
+        and its workspace: use one MonoKernel per stream, or order the launches."""
+        M = int(M)
+        dev = torch.device(device)
+        if dev.type == "cuda" and dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        arena = self._scratch.get(dev)
+        if arena is None or arena["tokens"] < M:
+            if dev.type == "cuda" and torch.cuda.is_current_stream_capturing():
+                return self._allocate_scratch(M, dev)
+            if arena is not None:
+                self._retired.append(arena)
+            arena = {"tokens": M, "buffers": self._allocate_scratch(M, dev), "views": {}}
+            self._scratch[dev] = arena
+        sc = arena["views"].get(M)
         if sc is None:
-            K, H, k = geo["k_dim"], geo["h_dim"], geo["top_k"]
-            sc = {
-                "workspace": torch.zeros(geo["workspace_bytes"], dtype=torch.uint8, device=device),
-                "act_fp8": torch.empty(M, K, dtype=torch.uint8, device=device),
-                "act_scales": torch.empty(M, K // 128, dtype=torch.float32, device=device),
-                "topk_ids": torch.empty(M, k, dtype=torch.int32, device=device),
-                "topk_weights": torch.empty(M, k, dtype=torch.float32, device=device),
-                "sorted_ids": torch.empty(M * k, dtype=torch.int32, device=device),
-                "partial": torch.empty(M * k * (self._int_symbol("partial_chunks") or 1), H, dtype=torch.bfloat16, device=device),
-            }
-            if len(self._scratch) >= 4:
-                self._scratch.pop(next(iter(self._scratch)))
-            self._scratch[key] = sc
+            buf, k = arena["buffers"], self.geometry()["top_k"]
+            chunks = self._int_symbol("partial_chunks") or 1
+            sc = {"workspace": buf["workspace"], "act_fp8": buf["act_fp8"][:M], "act_scales": buf["act_scales"][:M],
+                  "topk_ids": buf["topk_ids"][:M], "topk_weights": buf["topk_weights"][:M],
+                  "sorted_ids": buf["sorted_ids"][:M * k], "partial": buf["partial"][:M * k * chunks]}
+            arena["views"][M] = sc
         return sc
 
     def check_status(self, workspace: torch.Tensor) -> None:
