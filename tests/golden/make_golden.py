@@ -22,9 +22,7 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-if len(sys.argv) < 2:
-    raise SystemExit("usage: make_golden.py <path of a checkout of the reference repository>")
-REF = sys.argv[1]
+REF = sys.argv[1] if len(sys.argv) > 1 and __name__ == "__main__" else None
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from unimonomoe_b200 import synth  # noqa: E402
 
@@ -104,6 +102,39 @@ def moe_golden():
           "EP parts sum error", float((parts[0] + parts[1] - ref).abs().max()))
 
 
+SLAB_SPEC = dict(hidden=2048, inter=512, experts=4, top_k=2)   # the Qwen layer's slab counts: 16 K slabs up, 4 down
+SLAB_SEED, SLAB_TOKENS = 11, 48
+
+
+def slab_case():
+    """Inputs of the slab-count golden case, rebuilt from seeds (the 12 MB of weights are not stored)."""
+    spec = synth.LayerSpec("golden-slabs", **SLAB_SPEC)
+    layer = synth.make_layer(spec, seed=SLAB_SEED, chunk=4, with_shared=False)
+    g = torch.Generator().manual_seed(1234)
+    hs = torch.randn(SLAB_TOKENS, spec.hidden, generator=g).to(torch.bfloat16)
+    logits = torch.randn(SLAB_TOKENS, spec.experts, generator=g)
+    top = torch.topk(logits, spec.top_k, dim=1)
+    tw = torch.softmax(logits, 1).gather(1, top.indices)
+    tw = (tw / tw.sum(1, keepdim=True)).float()
+    return spec, layer, hs, top.indices, tw
+
+
+def moe_slab_golden():
+    """The reference's fp64 oracle on a case with the real layer's slab counts (K = 2048, I = 512), so that the
+    path-faithful tier can be held to the accuracy band the reference publishes for its kernel."""
+    spec, layer, hs, ids, tw = slab_case()
+    env = dict(torch=torch, DEV="cpu", E=spec.experts, TOP_K=spec.top_k, H_DIM=spec.hidden, K_DIM=spec.hidden,
+               N_HALF=spec.inter, N_UP=2 * spec.inter, E_LOCAL=spec.experts)
+    lift(os.path.join(REF, "research_archive/ds3_acc.py"), ["dequant", "oracle", "rel_cos"], env)
+    L = dict(w13=layer["w13"], w13s=layer["w13_scale"], w2=layer["w2"], w2s=layer["w2_scale"])
+    ref = env["oracle"](hs, L, ids, tw)
+    digest = int(layer["w13"].view(torch.uint8).long().sum() * 31 + layer["w2"].view(torch.uint8).long().sum())
+    np.savez_compressed(os.path.join(HERE, "moe_slabs.npz"), ref_fp64=ref.numpy(), ids=ids.numpy().astype(np.int32),
+                        weights=tw.numpy(), hs_bf16=hs.view(torch.int16).numpy(), weight_digest=np.int64(digest),
+                        w13_scale=layer["w13_scale"].numpy(), w2_scale=layer["w2_scale"].numpy())
+    print("moe_slabs.npz written; |ref| rms", float(ref.pow(2).mean().sqrt()))
+
+
 def e4m3_golden():
     codes = torch.arange(256, dtype=torch.uint8)
     dec = codes.view(torch.float8_e4m3fn).float()
@@ -116,6 +147,9 @@ def e4m3_golden():
 
 
 if __name__ == "__main__":
+    if REF is None:
+        raise SystemExit("usage: make_golden.py <path of a checkout of the reference repository>")
     routing_golden()
     moe_golden()
+    moe_slab_golden()
     e4m3_golden()

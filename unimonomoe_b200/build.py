@@ -25,6 +25,9 @@ DS = dict(K=7168, H=7168, MODE=2)
 # E_LOCAL the experts whose weights this rank holds.
 VARIANTS = {
     "qwen_w1": dict(QWEN, N_HALF=512, E_LOCAL=256),   # Qwen3.5-35B-A3B-like, one GPU
+    # the same geometry with the plain sigmoid + bias router (ROUTER_MODE 1 of the reference,
+    # kernel/qwen_tp/src/prefill_mono_final_nb.cu:134-150): no expert groups
+    "qwen_sig_w1": dict(QWEN, N_HALF=512, E_LOCAL=256, MODE=1),
     "qwen_tp2": dict(QWEN, N_HALF=256, E_LOCAL=256),
     "qwen_tp4": dict(QWEN, N_HALF=128, E_LOCAL=256),
     "qwen_ep2": dict(QWEN, N_HALF=512, E_LOCAL=128),
