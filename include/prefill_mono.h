@@ -1,8 +1,11 @@
 /* C ABI of libprefill_mono_<variant>.so -- the drop-in boundary of the FP8 MoE prefill
  * kernel. Plain pointers and sizes only; every launch is asynchronous on the caller's
- * stream, allocates nothing and keeps no state between calls. The caller owns every
- * buffer, including the workspace. The symbols, argument order and return codes are the
- * ones the reference's loader binds with ctypes
+ * stream and allocates nothing. For the reference's entry points the caller owns every
+ * buffer, including the workspace, and the library keeps nothing between calls except a
+ * table of TMA descriptors keyed by the weights' addresses (prefill_wgmma_plan_*), the
+ * wait time limit and the debug pointers set through the setters below;
+ * launch_prefill_moe_noalloc alone keeps its scratch inside the library. The symbols,
+ * argument order and return codes are the ones the reference's loader binds with ctypes
  * (vllm_integration/vllm/_custom_ops.py:4274-4288, :4705-4743), so its gates and its vLLM
  * quant-method hook work against this library unchanged.
  *
@@ -22,7 +25,10 @@
  *  -121      non-expert-parallel build called with an expert map
  *  -2 / -3   tensor-map encoding failed (up / down weights)
  *  > 0       cudaError_t
- * All negative codes are returned before any CUDA call is made.
+ * -100, -120, -121, -101, -102, -104, -110..-114 are returned, in this order of checking (EP:1650-1683),
+ * before any CUDA call is made; -103 follows the query of the device's SM count, -2 / -3 / -4 the
+ * descriptor encoding, -107 the cluster occupancy query. Nothing has been enqueued when a negative
+ * code comes back.
  *
  * Buffers (T = num_tokens, k = top_k = 8, E = 256 routed experts, El = local experts):
  *   logits            fp32 [T, E]                      in
@@ -165,6 +171,18 @@ int launch_prefill_moe_wgmma_q1_gemv(const void* router_w_bf16, float* logits_ou
                                      void* tp_seqctr, const void* tp_residual, float out_scale,
                                      const int32_t* expert_map, prefill_mono_stream_t stream);
 
+/* Plan / run split (the reference rebuilds both TMA descriptors and re-sets the kernel attribute on every
+ * call, Q:1611-1639, 1655; docs/FLASHINFER_UPSTREAM_NOTES.md:42-46 asks for the split). Descriptors are kept in
+ * a table keyed by the tensors' addresses and found again by every later launch; the kernel's shared-memory
+ * attribute is set once per device. prefill_wgmma_plan_prepare does both ahead of the first launch of a layer
+ * (optional: an unprepared layer is prepared by its first launch). Returns 0, -104 (null), -2 / -3, or a
+ * cudaError_t. prefill_wgmma_plan_stats reports look-ups served from the table / encoded anew;
+ * prefill_wgmma_plan_reset forgets every descriptor (call it when weights are freed and their addresses may be
+ * reused by tensors of another shape). */
+int prefill_wgmma_plan_prepare(const uint8_t* up_w_fp8, const uint8_t* down_w_fp8);
+void prefill_wgmma_plan_stats(unsigned long long* hits, unsigned long long* misses);
+void prefill_wgmma_plan_reset(void);
+
 int prefill_wgmma_arch(void);                 /* 100 = built for sm_100a */
 /* 1 = tiles run as pairs on clusters of two CTAs (tcgen05 cta_group::2); the total_tiles word of the
  * workspace then counts pairs, and launch_prefill_moe_wgmma_q1_gemv returns -106 (no router linear).
@@ -209,6 +227,11 @@ int launch_prefill_moe_noalloc(const float* logits, int num_tokens, const void* 
                                prefill_mono_stream_t stream);
 int prefill_wgmma_noalloc_max_tokens(void);
 size_t prefill_wgmma_noalloc_scratch_bytes(void);
+/* The four status words (status, abort flag, two detail words) of the last launch_prefill_moe_noalloc on the
+ * current device, copied to out[0..3] on `stream`: that entry's workspace is inside the library, so this is how
+ * its caller sees a bounded wait that gave up (out[0] == 0: success). Enqueue it behind the launch on the same
+ * stream and read `out` after synchronising. -131 before the first launch on this device. */
+int prefill_wgmma_noalloc_status(uint32_t* out, prefill_mono_stream_t stream);
 
 #ifdef __cplusplus
 }

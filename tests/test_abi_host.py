@@ -109,6 +109,24 @@ def test_expert_parallel_build_declines_without_map(built_libs):
     assert lib.launch_prefill_moe_wgmma_q1(*a) == -120          # the pre-existing ABI forwards a null map
     a, keep = _args(extra=[ctypes.c_void_p(0), ctypes.c_void_p(0)])
     assert lib.launch_prefill_moe_wgmma_q1_ep(*a) == -120
+    # order of the checks as in the reference (kernel/qwen_ep/src/prefill_mono_final_nb.cu:1650-1660): the
+    # workspace first, then the map against the build, then the token count
+    a, keep = _args(ws_bytes=16)
+    assert lib.launch_prefill_moe_wgmma_q1(*a) == -100
+    a, keep = _args(n_tokens=0)
+    assert lib.launch_prefill_moe_wgmma_q1(*a) == -120
+
+
+def test_plan_symbols_without_a_device(built_libs):
+    """The plan step needs a driver to encode descriptors; without one it must fail with a code, not crash,
+    and the look-up statistics must be readable."""
+    lib = MonoKernel(built_libs["qwen_w1"]).lib
+    lib.prefill_wgmma_plan_prepare.restype = ctypes.c_int
+    assert lib.prefill_wgmma_plan_prepare(ctypes.c_void_p(0), ctypes.c_void_p(0)) == -104
+    hits, misses = ctypes.c_ulonglong(7), ctypes.c_ulonglong(7)
+    lib.prefill_wgmma_plan_stats(ctypes.byref(hits), ctypes.byref(misses))
+    assert hits.value == 0
+    lib.prefill_wgmma_plan_reset()
 
 
 def test_pad_words_and_caps(built_libs):

@@ -548,3 +548,67 @@ def test_tiny_batches_repeated(gu, qwen_full):
                     first = out.clone()
                 assert torch.equal(out.view(torch.int16), first.view(torch.int16))
         mk.check_status(mk.scratch(T, gu.DEV)["workspace"])
+
+
+def test_descriptors_are_made_once_per_weight_tensor(gu, qwen_full):
+    """Plan / run split: the TMA descriptors of a layer's weights are encoded at the first launch (or by
+    prefill_wgmma_plan_prepare) and found again by every later one; a second layer adds its own two."""
+    mk = gu.kernel("qwen_w1")
+    lib = mk.lib
+    lib.prefill_wgmma_plan_prepare.restype = ctypes.c_int
+
+    def stats():
+        h, m = ctypes.c_ulonglong(), ctypes.c_ulonglong()
+        lib.prefill_wgmma_plan_stats(ctypes.byref(h), ctypes.byref(m))
+        return h.value, m.value
+
+    lib.prefill_wgmma_plan_reset()
+    h0, m0 = stats()
+    assert lib.prefill_wgmma_plan_prepare(ctypes.c_void_p(qwen_full["w13"].data_ptr()),
+                                          ctypes.c_void_p(qwen_full["w2"].data_ptr())) == 0
+    h1, m1 = stats()
+    assert m1 - m0 == 2 and h1 == h0
+    batch = synth.make_batch(synth.QWEN, qwen_full, 300, seed=31, device=gu.DEV)
+    first = gu.launch(mk, qwen_full, batch)["out"].clone()
+    for _ in range(5):
+        again = gu.launch(mk, qwen_full, batch)["out"]
+        assert torch.equal(first.view(torch.int16), again.view(torch.int16))
+    h2, m2 = stats()
+    assert m2 == m1 and h2 - h1 == 12          # six launches, two look-ups each, nothing encoded again
+    other = {k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in qwen_full.items()}
+    gu.launch(mk, other, batch)
+    assert stats()[1] == m2 + 2
+
+
+def test_captured_graph_survives_other_batch_sizes(gu, qwen_full):
+    """A captured launch holds the addresses of its scratch. Launches of five other sizes through the same
+    MonoKernel, one of them larger than anything seen before (which makes the scratch arena grow), must
+    leave that memory alone: the replay afterwards still reproduces the eager result bit for bit."""
+    from unimonomoe_b200 import MonoKernel, variant_path
+    mk = MonoKernel(variant_path("qwen_w1"))          # a fresh object: its arena starts empty
+    T = 640
+    batch = synth.make_batch(synth.QWEN, qwen_full, T, seed=41, device=gu.DEV)
+    w = (qwen_full["w13"], qwen_full["w13_scale"], qwen_full["w2"], qwen_full["w2_scale"])
+    eager = torch.empty(T, 2048, dtype=torch.bfloat16, device=gu.DEV)
+    mk.prefill_impl(batch["hs"], batch["logits"], *w, 8, True, None, eager, check=True)
+    out = torch.empty(T, 2048, dtype=torch.bfloat16, device=gu.DEV)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        mk.prefill_impl(batch["hs"], batch["logits"], *w, 8, True, None, out)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        mk.prefill_impl(batch["hs"], batch["logits"], *w, 8, True, None, out)
+    for other in (100, 200, 333, 512, 2000):       # 2000 > 640: a larger arena is added, the old one is kept
+        b2 = synth.make_batch(synth.QWEN, qwen_full, other, seed=other, device=gu.DEV)
+        o2 = torch.empty(other, 2048, dtype=torch.bfloat16, device=gu.DEV)
+        mk.prefill_impl(b2["hs"], b2["logits"], *w, 8, True, None, o2, check=True)
+        junk = torch.full((other * 8, 2048), float("nan"), dtype=torch.bfloat16, device=gu.DEV)   # churn the allocator
+        del junk
+    assert len(mk._retired) == 1
+    out.fill_(float("nan"))
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), eager.view(torch.int16))

@@ -7,6 +7,7 @@
 // (kernel/moe_monokernel/src/moe_grid_barrier.h:101-199,
 // kernel/qwen_tp/src/prefill_mono_final_nb.cu:244-247, :1468, :1500).
 #pragma once
+#include <cstddef>
 #include <cstdint>
 #include "ptx_sm100.cuh"
 
@@ -27,26 +28,30 @@ enum StatusCode : uint32_t {
   kErrBounds = 6,        // an index computed on the device fell outside its buffer
 };
 
-// Everything is a 4-byte word except the 8-byte time stamps at the (8-byte aligned) end.
+// Everything is a 4-byte word except the 8-byte time stamps at the (8-byte aligned) end. The words a launch
+// needs at zero come first (kWorkspaceZeroBytes of them): the launcher clears only those; everything behind
+// them is written in full by the kernel before it is read.
 struct Workspace {
   uint32_t barrier[kBarrierSites];          // arrival counters, one per barrier site, used once per launch
   uint32_t status;                          // 0 = ok, else (code << 24) | (site << 16) | block
   uint32_t abort_flag;                      // raised together with status
   uint32_t status_aux[2];                   // free-form detail for the first error
+  uint32_t tp_ready[kTpMaxChunks];          // compute blocks that finished chunk c
+  uint32_t tp_done_local;                   // communication blocks past their last shard
+  uint32_t tp_done_flag;                    // set once the final rank barrier is past
+  uint32_t tp_seq_pub;                      // this launch's sequence number
+  uint32_t reserved2;
+  // ---- end of the part the launcher zeroes
   int32_t total_tiles;                      // tiles of 128 sorted rows in this launch
   int32_t reserved0[3];
   int32_t expert_counts[kNumExperts];       // rows routed to each local expert
   int32_t expert_offsets[kNumExperts + 1];  // exclusive prefix sum of expert_counts
   int32_t reserved1[3];
   int32_t cta_hist[kGrid][kNumExperts];     // per-CTA histograms (basis of the stable scatter)
-  uint32_t tp_ready[kTpMaxChunks];          // compute blocks that finished chunk c
-  uint32_t tp_done_local;                   // communication blocks past their last shard
-  uint32_t tp_done_flag;                    // set once the final rank barrier is past
-  uint32_t tp_seq_pub;                      // this launch's sequence number
-  uint32_t reserved2;
   uint64_t phase_ns[8];                     // %globaltimer at phase boundaries, written by block 0
   uint64_t prof[kGrid][16];                 // per-CTA stall counters (cycles), filled only by MONO_PROFILE builds
 };
+constexpr size_t kWorkspaceZeroBytes = offsetof(Workspace, total_tiles);
 
 struct WaitCtx {
   Workspace* ws;

@@ -39,6 +39,8 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
+#include <unordered_map>
 
 #include "bounded_wait.cuh"
 #include "pair_sm100.cuh"
@@ -1726,6 +1728,56 @@ int make_bf16_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// Plan / run split. What a launch needs besides its arguments depends only on the device (the kernel's
+// shared-memory attribute) and on the weight tensors (their TMA descriptors: base address + the compiled
+// extents). Both are made once and kept: a descriptor per (kind, base address, rows) in a small table, the
+// attribute once per device. The reference re-encodes both descriptors and re-sets the attribute on every
+// call (kernel/qwen_tp/src/prefill_mono_final_nb.cu:1611-1639, :1655).
+struct MapKey {
+  const void* base;
+  uint64_t rows;
+  int kind;  // 0 up weights, 1 down weights, 2 activations (router), 3 router weight
+  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && kind == o.kind; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.base) ^ (std::hash<uint64_t>()(k.rows) * 1000003u) ^ static_cast<size_t>(k.kind) << 1;
+  }
+};
+std::mutex g_plan_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+unsigned long long g_map_hits = 0, g_map_misses = 0;
+constexpr size_t kMaxCachedMaps = 4096;   // far more than the MoE layers of a model; beyond it the table restarts
+bool g_attr_set[64] = {};
+
+// Copies the cached descriptor into *dst, encoding it first if this tensor has not been seen.
+int cached_map(CUtensorMap* dst, int kind, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  const MapKey key{base, rows, kind};
+  std::lock_guard<std::mutex> lock(g_plan_mutex);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    ++g_map_hits;
+    *dst = it->second;
+    return 0;
+  }
+  ++g_map_misses;
+  CUtensorMap m;
+  const int rc = (kind <= 1) ? make_u8_map(&m, base, rows, cols, box_rows) : make_bf16_map(&m, base, rows, cols, box_rows);
+  if (rc != 0) return rc;
+  if (g_maps.size() >= kMaxCachedMaps) g_maps.clear();
+  g_maps.emplace(key, m);
+  *dst = m;
+  return 0;
+}
+
+cudaError_t ensure_kernel_attribute(int dev) {
+  std::lock_guard<std::mutex> lock(g_plan_mutex);
+  if (dev >= 0 && dev < 64 && g_attr_set[dev]) return cudaSuccess;
+  const cudaError_t err = cudaFuncSetAttribute(moe_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM);
+  if (err == cudaSuccess && dev >= 0 && dev < 64) g_attr_set[dev] = true;
+  return err;
+}
+
 }  // namespace
 }  // namespace mono
 
@@ -1791,6 +1843,32 @@ void prefill_wgmma_set_debug(void* acc, void* inter, void* inter_scale) {
   g_dbg_inter_scale = static_cast<float*>(inter_scale);
 }
 
+// Plan step, optional: make (or find) the descriptors of a layer's weights and set the kernel's attribute on
+// the current device now, so that the first launch of that layer does not pay for it. Launches look the
+// descriptors up by the weights' addresses; a layer that was never prepared is prepared by its first launch.
+// Returns 0, -2 / -3 (descriptor encoding failed) or a cudaError_t.
+int prefill_wgmma_plan_prepare(const uint8_t* up_w_fp8, const uint8_t* down_w_fp8) {
+  if (up_w_fp8 == nullptr || down_w_fp8 == nullptr) return -104;
+  CUtensorMap tmp;
+  if (cached_map(&tmp, 0, up_w_fp8, static_cast<uint64_t>(E_LOCAL) * N_UP, K_DIM, HCB) != 0) return -2;
+  if (cached_map(&tmp, 1, down_w_fp8, static_cast<uint64_t>(E_LOCAL) * H_DIM, N_HALF, HCB) != 0) return -3;
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err == cudaSuccess) err = ensure_kernel_attribute(dev);
+  return static_cast<int>(err);
+}
+// Descriptor look-ups served from the table / encoded anew since the library was loaded.
+void prefill_wgmma_plan_stats(unsigned long long* hits, unsigned long long* misses) {
+  std::lock_guard<std::mutex> lock(g_plan_mutex);
+  if (hits != nullptr) *hits = g_map_hits;
+  if (misses != nullptr) *misses = g_map_misses;
+}
+// Forget every cached descriptor (weights were freed and their addresses will be reused for other shapes).
+void prefill_wgmma_plan_reset() {
+  std::lock_guard<std::mutex> lock(g_plan_mutex);
+  g_maps.clear();
+}
+
 // Common launcher. router_w == nullptr: `logits` holds the caller's router logits. Otherwise
 // router_w is the bf16 router weight [E, K] and `logits` is the [T, E] fp32 buffer the kernel fills.
 static int launch_common(const void* router_w, float* logits_buf, const float* logits, int num_tokens, int block_m,
@@ -1806,9 +1884,10 @@ static int launch_common(const void* router_w, float* logits_buf, const float* l
   (void)block_m;  // the tile height is the compiled TILE_M
   if (router_w != nullptr && PAIR) return -106;  // the pair build has no router linear
   if (router_w != nullptr) logits = logits_buf;
+  // order of the checks as in kernel/qwen_ep/src/prefill_mono_final_nb.cu:1650-1660
+  if (workspace == nullptr || workspace_bytes < sizeof(Workspace)) return -100;
   if (EP_BUILD && expert_map == nullptr) return -120;
   if (!EP_BUILD && expert_map != nullptr) return -121;
-  if (workspace == nullptr || workspace_bytes < sizeof(Workspace)) return -100;
   if (num_tokens <= 0) return -101;
   const long long numel = static_cast<long long>(num_tokens) * TOP_K;
   if ((numel / TILE_M + E_LOCAL) * NCH > MAX_TILES) return -102;
@@ -1864,29 +1943,30 @@ static int launch_common(const void* router_w, float* logits_buf, const float* l
   p.dbg_inter = g_dbg_inter;
   p.dbg_inter_scale = g_dbg_inter_scale;
 
-  int rc = make_u8_map(&p.tm_up, up_w_fp8, static_cast<uint64_t>(E_LOCAL) * N_UP, K_DIM, HCB);
+  int rc = cached_map(&p.tm_up, 0, up_w_fp8, static_cast<uint64_t>(E_LOCAL) * N_UP, K_DIM, HCB);
   if (rc != 0) {
     fprintf(stderr, "up-projection tensor map failed: %d\n", rc);
     return -2;
   }
-  rc = make_u8_map(&p.tm_down, down_w_fp8, static_cast<uint64_t>(E_LOCAL) * H_DIM, N_HALF, HCB);
+  rc = cached_map(&p.tm_down, 1, down_w_fp8, static_cast<uint64_t>(E_LOCAL) * H_DIM, N_HALF, HCB);
   if (rc != 0) {
     fprintf(stderr, "down-projection tensor map failed: %d\n", rc);
     return -3;
   }
   if (router_w != nullptr) {
     p.logits_out = logits_buf;
-    rc = make_bf16_map(&p.tm_x, act_bf16, static_cast<uint64_t>(num_tokens), K_DIM, TILE_M);
-    if (rc == 0) rc = make_bf16_map(&p.tm_rw, router_w, E, K_DIM, E);
+    rc = cached_map(&p.tm_x, 2, act_bf16, static_cast<uint64_t>(num_tokens), K_DIM, TILE_M);
+    if (rc == 0) rc = cached_map(&p.tm_rw, 3, router_w, E, K_DIM, E);
     if (rc != 0) {
       fprintf(stderr, "router tensor map failed: %d\n", rc);
       return -4;
     }
   }
 
-  err = cudaFuncSetAttribute(moe_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM);
+  err = ensure_kernel_attribute(dev);
   if (err != cudaSuccess) return static_cast<int>(err);
-  err = cudaMemsetAsync(workspace, 0, sizeof(Workspace), stream);
+  // only the head of the workspace has to start at zero (barrier counters, status, chunk counters)
+  err = cudaMemsetAsync(workspace, 0, kWorkspaceZeroBytes, stream);
   if (err != cudaSuccess) return static_cast<int>(err);
 
   if constexpr (PAIR) {
@@ -2063,7 +2143,46 @@ constexpr size_t kNaBytes = kNaPartial + na_align(static_cast<size_t>(kNoAllocMa
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNaBytes];
 
+// Device address of the array on the current device; resolved on first use when `resolve` is set.
+static int noalloc_base(unsigned char** out, bool resolve) {
+  constexpr int kMaxDevices = 64;
+  static unsigned char* base_of_device[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  const cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  if (dev < 0 || dev >= kMaxDevices) return -131;
+  std::lock_guard<std::mutex> lock(mu);
+  if (base_of_device[dev] == nullptr && resolve) {
+    // In host code the array's name is only a handle: the device address has to be asked for, once per
+    // device, with that device current.
+    void* ptr = nullptr;
+    const cudaError_t e2 = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e2 != cudaSuccess || ptr == nullptr) {
+      fprintf(stderr, "launch_prefill_moe_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e2));
+      return -131;
+    }
+    base_of_device[dev] = static_cast<unsigned char*>(ptr);
+  }
+  if (base_of_device[dev] == nullptr) return -131;
+  *out = base_of_device[dev];
+  return 0;
+}
+
 int prefill_wgmma_noalloc_max_tokens() { return kNoAllocMaxTokens; }
+// The status words (status, abort flag, two detail words) of the last launch_prefill_moe_noalloc on the
+// current device, copied to out[0..3] on `stream`: the workspace of that entry is inside the library, so this
+// is how its caller learns of a bounded wait that gave up. out[0] == 0 means success. Enqueue it behind the
+// launch on the same stream and read `out` after synchronising (pinned memory makes the copy asynchronous).
+// -131 before the first launch on this device; otherwise 0 or a cudaError_t.
+int prefill_wgmma_noalloc_status(uint32_t* out, cudaStream_t stream) {
+  if (out == nullptr) return -104;
+  unsigned char* b = nullptr;
+  const int rc = noalloc_base(&b, false);
+  if (rc != 0) return rc;
+  return static_cast<int>(cudaMemcpyAsync(out, b + kNaWorkspace + offsetof(Workspace, status), 16,
+                                          cudaMemcpyDeviceToHost, stream));
+}
 size_t prefill_wgmma_noalloc_scratch_bytes() { return kNaBytes; }
 
 // Returns 0 on success; -130 when num_tokens exceeds prefill_wgmma_noalloc_max_tokens(); -131 when the
@@ -2077,24 +2196,9 @@ int launch_prefill_moe_noalloc(const float* logits, int num_tokens, const void* 
             kNoAllocMaxTokens);
     return -130;
   }
-  // In host code the array's name is only a handle: the device address has to be asked for, once per
-  // device, with that device current.
-  constexpr int kMaxDevices = 64;
-  static unsigned char* base_of_device[kMaxDevices] = {};
-  int dev = 0;
-  cudaError_t err = cudaGetDevice(&dev);
-  if (err != cudaSuccess) return static_cast<int>(err);
-  if (dev < 0 || dev >= kMaxDevices) return -131;
-  if (base_of_device[dev] == nullptr) {
-    void* ptr = nullptr;
-    err = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
-    if (err != cudaSuccess || ptr == nullptr) {
-      fprintf(stderr, "launch_prefill_moe_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(err));
-      return -131;
-    }
-    base_of_device[dev] = static_cast<unsigned char*>(ptr);
-  }
-  unsigned char* b = base_of_device[dev];
+  unsigned char* b = nullptr;
+  const int rc = noalloc_base(&b, true);
+  if (rc != 0) return rc;
   return launch_prefill_moe_wgmma_q1_ep2(
       logits, num_tokens, TILE_M, b + kNaWorkspace, sizeof(Workspace), act_bf16, b + kNaActFp8,
       reinterpret_cast<float*>(b + kNaActScales), up_w_fp8, up_w_scales, down_w_fp8, down_w_scales,
