@@ -612,3 +612,28 @@ def test_captured_graph_survives_other_batch_sizes(gu, qwen_full):
     g.replay()
     torch.cuda.synchronize()
     assert torch.equal(out.view(torch.int16), eager.view(torch.int16))
+
+
+@pytest.mark.parametrize("rank", [0, 5])
+def test_deepseek_expert_parallel_8_rank_in_sequence(gu, oracle, rank):
+    """DeepSeek-V3 geometry under EP = 8: 32 local experts at the full intermediate width of 2048 columns (the
+    configuration in which the reference ran out of shared memory, research_archive/reports/
+    ds3_ep_monokernel_result.md:118-153), here processed in four chunks of 512. One rank at a time on one GPU:
+    grouped sigmoid routing with the global-to-local map bit-exact, output against the oracle."""
+    spec, mk = synth.DEEPSEEK, gu.kernel("ds_ep8")
+    geo = mk.geometry()
+    assert geo["num_experts_local"] == 32 and geo["n_half"] == 2048 and mk._int_symbol("partial_chunks") == 4
+    layer = synth.make_layer(spec, seed=0, device=gu.DEV, expert_slice=(32 * rank, 32 * rank + 32), with_shared=False, chunk=8)
+    emap = synth.expert_map(spec, rank, 8, device=gu.DEV)
+    for T in (200, 4096):
+        batch = synth.make_batch(spec, layer, T, seed=2, device=gu.DEV)
+        res = gu.launch(mk, layer, batch, expert_map=emap)
+        ids, w, gids = gu.check_routing(oracle, res, batch, 2, layer["bias"], 32, expert_map=emap, rows_per_unit=None)
+        q, s = gu.check_act_quant(oracle, res, batch)
+        assert res["ids"].min() >= -1 and res["ids"].max() < 32
+        owned = (res["ids"] >= 0).sum()
+        assert 0 < owned < T * 8
+        assert torch.isfinite(res["out"].float()).all()
+        gu.check_output(oracle, res["out"], gu.sample_tokens(T, 24, rank), q, s, ids, w, layer)
+    del layer
+    torch.cuda.empty_cache()

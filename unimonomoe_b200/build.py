@@ -37,6 +37,10 @@ VARIANTS = {
     "ds_tp4": dict(DS, N_HALF=512, E_LOCAL=256),
     "ds_tp2": dict(DS, N_HALF=1024, E_LOCAL=256),     # intermediate processed in 2 chunks of 512 columns
     "ds_w1": dict(DS, N_HALF=2048, E_LOCAL=256),      # full width on one GPU: 4 chunks
+    # DeepSeek-V3 expert parallel over 8 ranks: 32 local experts at full width. The reference stopped here
+    # because the [128, 2048] e4m3 intermediate does not fit in shared memory
+    # (research_archive/reports/ds3_ep_monokernel_result.md:118-153); processed in 4 chunks of 512 columns
+    "ds_ep8": dict(DS, N_HALF=2048, E_LOCAL=32),
     # tiles scheduled as pairs on clusters of two CTAs (tcgen05 cta_group::2); measured equal in speed to
     # qwen_w1 at 16384 tokens (fewer L2 weight bytes per SM, but 11 % more padded rows), so not the default
     "qwen_w1_pair": dict(QWEN, N_HALF=512, E_LOCAL=256, PAIR=1),
