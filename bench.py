@@ -666,9 +666,16 @@ def verify_reduced_output(spec, mk, layer, batch, emap, sc, pool_plan, result, w
                                                            chunk=shard_kw.get("chunk", 16), **kw_r)
             tot += O.moe_path(toks, q, s, ids_r, w, sh["w13"], sh["w13_scale"], sh["w2"], sh["w2_scale"]).float()
             del sh
-        m = O.parity_metrics(got.float().cpu()[torch.from_numpy(toks).long()], tot)
-        info["oracle"] = {"tokens": n_tok, **m}
-        ok = ok and m["max_abs_over_rms"] <= 2e-2 and m["cos"] >= 0.9995
+        mine = got.float().cpu()[torch.from_numpy(toks).long()]
+        m = O.parity_metrics(mine, tot)
+        # every element within 2e-2 rms, or (the output is bf16: above 3 rms one bf16 step is wider than that)
+        # within one bf16 step per rank's rounding plus the final one
+        err = (mine - tot).abs()
+        beyond = err > 2e-2 * m["rms_ref"]
+        step = torch.exp2(torch.floor(torch.log2(tot.abs().clamp(min=2.0 ** -126))) - 7.0)
+        within_steps = bool((err[beyond] <= step[beyond] * (world + 1) * 1.0001).all())
+        info["oracle"] = {"tokens": n_tok, **m, "beyond_2e-2_rms": int(beyond.sum()), "those_within_bf16_steps": within_steps}
+        ok = ok and m["cos"] >= 0.9995 and within_steps and int(beyond.sum()) <= max(1, tot.numel() // 10000)
     flag = torch.tensor([1.0 if ok else 0.0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     info["ok"] = bool(flag.item() == 1.0)

@@ -249,9 +249,17 @@ def gates_for(rig: Rig, T: int, ncomm: int) -> dict:
                 ids_r = np.where((ids >= rr * n_e) & (ids < (rr + 1) * n_e), ids - rr * n_e, -1).astype(np.int32)
             tot += O.moe_path(toks, q, s, ids_r, w, sh["w13"], sh["w13_scale"], sh["w2"], sh["w2_scale"]).float()
             del sh
-        m = O.parity_metrics(ref.float().cpu()[torch.from_numpy(toks).long()], tot)
+        mine = ref.float().cpu()[torch.from_numpy(toks).long()]
+        m = O.parity_metrics(mine, tot)
+        # within 2e-2 rms, or -- the output is bf16, and above 3 rms one bf16 step is wider than that -- within
+        # one bf16 step per rank's rounding plus the final one; such elements have to be rare
+        err = (mine - tot).abs()
+        beyond = err > 2e-2 * m["rms_ref"]
+        step = torch.exp2(torch.floor(torch.log2(tot.abs().clamp(min=2.0 ** -126))) - 7.0)
+        m["beyond_2e-2_rms"] = int(beyond.sum())
         r["g7_oracle"] = m
-        r["g7_ok"] = bool(m["max_abs_over_rms"] <= 2e-2 and m["cos"] >= 0.9995)
+        r["g7_ok"] = bool(m["cos"] >= 0.9995 and (err[beyond] <= step[beyond] * (rig.world + 1) * 1.0001).all()
+                          and m["beyond_2e-2_rms"] <= max(1, tot.numel() // 10000))
     return r
 
 

@@ -140,3 +140,27 @@ def test_install_needs_a_binary(monkeypatch):
     monkeypatch.delenv("VLLM_PREFILL_MONOKERNEL_SO", raising=False)
     with pytest.raises(RuntimeError, match="no kernel binary"):
         vp.install()
+
+
+def test_install_attaches_the_hooks_to_the_installed_vllm(built_libs):
+    """With vLLM importable, install() gives its Fp8MoEMethod the three names the reference's runner looks up;
+    a quant method whose layer was never checked declines."""
+    pytest.importorskip("vllm")
+    try:
+        from vllm.model_executor.layers.quantization.fp8 import Fp8MoEMethod
+    except Exception as exc:
+        pytest.skip(f"this vLLM has no Fp8MoEMethod: {exc}")
+    before = Fp8MoEMethod.process_weights_after_loading
+    try:
+        assert vp.install(built_libs["qwen_w1"]) is True
+        for name in ("try_moe_monokernel", "monokernel_output_is_reduced", "monokernel_folds_shared_output"):
+            assert callable(getattr(Fp8MoEMethod, name))
+        assert Fp8MoEMethod.process_weights_after_loading is not before
+        bare = object.__new__(Fp8MoEMethod)
+        assert bare.try_moe_monokernel(None, None, None) is None
+        assert bare.monokernel_output_is_reduced() is False and bare.monokernel_folds_shared_output() is False
+    finally:
+        Fp8MoEMethod.process_weights_after_loading = before
+        for name in ("try_moe_monokernel", "monokernel_output_is_reduced", "monokernel_folds_shared_output"):
+            if name in Fp8MoEMethod.__dict__:
+                delattr(Fp8MoEMethod, name)

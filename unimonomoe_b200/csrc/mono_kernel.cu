@@ -131,10 +131,6 @@ static_assert(ROUTER_MODE != 2 || N_GROUP * 32 == E, "grouped routing assumes 32
 #ifndef MONO_NSPLIT
 #define MONO_NSPLIT 1
 #endif
-// Weight slabs requested into L2 ahead of the shared-memory loads (0: no prefetch).
-#ifndef MONO_PF_DIST
-#define MONO_PF_DIST 0
-#endif
 // MONO_PAIR=1: tiles are scheduled as pairs of 128-row tiles of one expert on a cluster of two CTAs
 // (tcgen05 cta_group::2, M = 256). Each CTA gathers its own 128 activation rows and loads HALF of every
 // weight stage; one thread of the cluster's rank-0 CTA issues the MMAs for both. Halves the weight
@@ -144,7 +140,6 @@ static_assert(ROUTER_MODE != 2 || N_GROUP * 32 == E, "grouped routing assumes 32
 #endif
 constexpr bool PAIR = MONO_PAIR != 0;
 constexpr int EPI_WGS = MONO_EPI_WGS;
-constexpr int PF_DIST = MONO_PF_DIST;
 static_assert(EPI_WGS == 2 || EPI_WGS == 4, "two or four epilogue warpgroups");
 static_assert(!PAIR || (EPI_WGS == 2 && MONO_NSPLIT == 1), "the pair schedule is written for two epilogue warpgroups, N = 256");
 // A 128-deep K slab of the 256 weight rows of a stage is issued as NSPLIT independent MMAs of
@@ -897,33 +892,6 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         uint32_t nb = 0;
         bool ok = true;
         PROF_DECL(pw_emptyB);
-        // A second cursor walks the same sequence of weight slabs PF_DIST slabs ahead of the loads and asks
-        // for them to be brought into L2: the operand ring holds only three slabs, too few to cover the
-        // latency of HBM, which every expert's weights come from the first time they are touched.
-        int pf_it = 0, pf_s = 0;
-        auto prefetch_next = [&]() {
-          if constexpr (PF_DIST > 0 && !PAIR) {
-            if (pf_it >= n_my) return;
-            const int e = S.tiles[pf_it].e, ch = S.tiles[pf_it].chunk;
-            if (pf_s < NP * NK) {
-              const int ps = pf_s / NK, ks = pf_s % NK;
-              const uint32_t yg = static_cast<uint32_t>(e * N_UP + ch * CHUNK_COLS + ps * 128);
-#pragma unroll
-              for (int c = 0; c < 128; c += HCB) {
-                tma_prefetch_l2_2d(&p.tm_up, static_cast<uint32_t>(ks * 128), yg + c);
-                tma_prefetch_l2_2d(&p.tm_up, static_cast<uint32_t>(ks * 128), yg + N_HALF + c);
-              }
-            } else {
-              const int sd = pf_s - NP * NK, hb = sd / NP, dk = sd % NP;
-              const uint32_t y = static_cast<uint32_t>(e * H_DIM + hb * 256);
-#pragma unroll
-              for (int j = 0; j < 256 / HCB; ++j)
-                tma_prefetch_l2_2d(&p.tm_down, static_cast<uint32_t>((ch * NP + dk) * 128), y + j * HCB);
-            }
-            if (++pf_s == NP * NK + NHB * NP) { pf_s = 0; ++pf_it; }
-          }
-        };
-        for (int i = 0; i < PF_DIST; ++i) prefetch_next();
         for (int it = 0; it < n_my && ok; ++it) {
           const int e = S.tiles[it].e, ch = S.tiles[it].chunk;
           for (int ps = 0; ps < NP && ok; ++ps) {
@@ -960,7 +928,6 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
                   tma_load_2d(&p.tm_up, x, yu + co, dst + (j * BC + hh * WC + HCB) * 128, &S.fullB[st]);
                 }
               }
-              prefetch_next();
               ++nb;
             }
           }
@@ -983,7 +950,6 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               if constexpr ((MONO_ABLATE & 16) != 0) { ++nb; continue; }
 #pragma unroll
               for (int j = 0; j < 256 / HCB; ++j) tma_load_2d(&p.tm_down, x, y + j * HCB, dst + j * HCB * 128, &S.fullB[st]);
-              prefetch_next();
               ++nb;
             }
           }
@@ -1105,7 +1071,6 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       // (TMA tile::gather4 was measured here as well: correct, but a third slower than this path
       // because every gathered row is a separate 128-byte request.)
       const int gt = tid - WARP_GATHER0 * 32;
-#ifndef MONO_GATHER_ROWWISE
       // Eight neighbouring lanes copy the eight 16-byte pieces of ONE row, so a warp instruction touches
       // 4 whole lines of global memory and 512 contiguous bytes of shared memory (one row per lane would be
       // 32 lines per instruction and a 4-way bank conflict). Thread g: piece g % 8 of rows g / 8 + 8 i.
@@ -1159,48 +1124,6 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       cp_async_commit();
       cp_async_wait<0>();
       if (gt == 0) { PROF_STORE(6, pg_emptyA); }
-#else
-      // one row per lane: thread g copies rows g and g+64
-      uint32_t na = 0;
-      bool ok = true;
-      PROF_DECL(pg_emptyA);
-      const uint32_t a_ring_u32 = smem_u32(a_ring);
-      for (int it = 0; it < n_my && ok; ++it) {
-        const TileInfo ti = S.tiles[it];
-        const uint8_t* src[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int r = gt + h * 64;
-          src[h] = nullptr;
-          if (r < ti.rows) {
-            const int fi = __ldcg(&p.sorted_ids[ti.row0 + r]);
-            if (fi >= 0 && fi < numel) src[h] = p.act_fp8 + static_cast<size_t>(fi / TOP_K) * K_DIM;
-          }
-        }
-        for (int s = 0; s < NP * NK; ++s) {
-          const int ks = s % NK;
-          const uint32_t sa = na % SA;
-          { PROF_T0();
-          if (!mbar_wait(&S.emptyA[sa], ((na / SA) & 1u) ^ 1u, wc, kSiteEmptyA)) { ok = false; break; }
-          PROF_ADD(pg_emptyA); }
-          const uint32_t dst = a_ring_u32 + sa * A_STAGE_BYTES;
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (src[h] != nullptr && (MONO_ABLATE & 8) == 0) {
-              const uint8_t* g = src[h] + ks * 128;
-#pragma unroll
-              for (int c = 0; c < 8; ++c) cp_async16(dst + sw128(gt + h * 64, c), g + c * 16);
-            }
-          }
-          // the barrier receives this thread's arrival when the copies above have landed
-          cp_async_arrive_noinc(&S.fullA[sa]);
-          ++na;
-        }
-      }
-      cp_async_commit();
-      cp_async_wait<0>();
-      if (gt == 0) { PROF_STORE(6, pg_emptyA); }
-#endif
     }
   } else {
     // ------------------------------------------------------------ epilogue (EPI_WGS x 128 threads)
@@ -1356,16 +1279,12 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
 #pragma unroll
             for (int i = 0; i < HCB / 2; ++i) {
               const float2 g = acc[j * (WC / 2) + i], u = acc[j * (WC / 2) + HCB / 2 + i];
-#ifdef MONO_SILU_TANH
-              // SiLU(g) * u = (u * g/2) * (1 + tanh(g/2)): one special-function operation per element instead of two
+              // SiLU(g) * u = (u * g/2) * (1 + tanh(g/2)): one special-function operation per element (tanh.approx,
+              // relative error 2^-11) where exp + division take two; the section is bound by that unit
               const float hx = 0.5f * g.x, hy = 0.5f * g.y;
               const float px = u.x * hx, py = u.y * hy;
               const float v0 = fmaf(px, tanh_approx(hx), px);
               const float v1 = fmaf(py, tanh_approx(hy), py);
-#else
-              const float v0 = __fdividef(u.x * g.x, 1.0f + __expf(-g.x));
-              const float v1 = __fdividef(u.y * g.y, 1.0f + __expf(-g.y));
-#endif
               acc[j * (WC / 2) + i] = make_float2(v0, v1);
               mx = fmaxf(mx, fmaxf(fabsf(v0), fabsf(v1)));
             }
@@ -1435,7 +1354,6 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             }
           }
           PROF_T0();
-#ifndef MONO_ST_ROWWISE
           // Neighbouring lanes swap half of their 32-byte pieces first, so that in every store instruction
           // lanes 2i and 2i+1 write 64 contiguous bytes of ONE row: 16 lines per instruction instead of 32.
           // (the guard is made warp-uniform: the shuffles below need every lane of the warp)
@@ -1472,27 +1390,6 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               }
             }
           }
-#else
-          if (fi >= 0 && !dead && (MONO_ABLATE & 4) == 0) {
-#pragma unroll
-            for (int j = 0; j < NSPLIT; ++j) {
-              __nv_bfloat16* dst = p.partial + (static_cast<size_t>(fi) * NCH + ti.chunk) * H_DIM + hb * 256 + j * BC + h * WC;
-#pragma unroll
-              for (int c = 0; c < WC / 16; ++c) {  // 16 bf16 = 32 bytes per store: whole sectors
-                uint32_t w[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  // times the routing weight, then bf16 with saturation to the largest finite value
-                  // (the clamp of kernel/qwen_tp/src/prefill_mono_final_nb.cu:916)
-                  const float2 v = __fmul2_rn(acc[j * (WC / 2) + c * 8 + i], rw2);
-                  w[i] = cvt_bf16x2_satfinite(v.x, v.y);
-                }
-                // written once, read once by the slot sum: keep it from pushing expert weights out of L2
-                st_global_256_stream(dst + c * 16, w);
-              }
-            }
-          }
-#endif
           if (has_next && hb >= 1 && hb - 1 < AS_PIECES) as_piece_store(hb - 1);
           PROF_ADD(pe_store);
         }

@@ -82,13 +82,6 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap* m, uint32_t x, ui
       : "memory");
 }
 
-// The same tile brought into L2 only (no shared-memory destination, no completion to wait for).
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, uint32_t x, uint32_t y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
-               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y)
-               : "memory");
-}
-
 // ---------------------------------------------------------------- cp.async (16 B, L2 only)
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
@@ -264,13 +257,9 @@ __device__ __forceinline__ void st_global_256(void* p, const uint32_t (&w)[8]) {
 
 // The same with the L2 evict-first priority, for data that is written once and read once much later.
 __device__ __forceinline__ void st_global_256_stream(void* p, const uint32_t (&w)[8]) {
-#ifdef MONO_PLAIN_STORES
-  st_global_256(p, w);
-#else
   asm volatile("st.global.L2::evict_first.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(w[0]), "r"(w[1]),
                "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
                : "memory");
-#endif
 }
 
 // ---------------------------------------------------------------- NVLS multimem
