@@ -244,6 +244,9 @@ def main() -> None:
                     help="after the timed steps, repeat the same launch for this long and report the steady-state "
                          "time and clocks (0: skip)")
     ap.add_argument("--no-verify", action="store_true", help="N>1: skip the pre-timing parity check (profiling runs)")
+    ap.add_argument("--chunks", type=int, default=0, help="N>1, in-kernel reduce: chunks the reduce is released in (0: table)")
+    ap.add_argument("--sweep", default="", help="N>1, in-kernel reduce: time these 'chunks:ncomm' pairs (comma separated) "
+                                                "after the contract line's own run and print them on stderr")
     ap.add_argument("--router", default="logits", choices=["logits", "gemv"],
                     help="logits: the caller's router logits go in (the reference's interface); gemv: the bf16 gate "
                          "weight goes in and the router linear runs inside the launch (no logits cross PCIe in e2e)")
@@ -311,7 +314,9 @@ def main() -> None:
     if world > 1:
         # the symmetric pool is built even when NCCL reduces: the parity check before the timing uses it
         plan = tp_fused.FusedTPPlan(mk, dist.group.WORLD, hidden=spec.hidden, max_tokens=T, nslots=2)
-        if plan.usable and plan.chunks_for(T) == 0:
+        if plan.usable and args.chunks > 0:
+            plan.chunks_by_tokens[T] = args.chunks
+        elif plan.usable and plan.chunks_for(T) == 0:
             plan.chunks_by_tokens[T] = 8 if T >= 16384 else 4
         if not plan.usable:
             if rank == 0:
@@ -396,6 +401,9 @@ def main() -> None:
         sustained = run_sustained(args.sustained_seconds, ms_per_step, launch, reduce_out, batch, barrier, world, dist, dev,
                                   physical_gpu_index(local), flops)
         mk.check_status(sc["workspace"])
+
+    if args.sweep and plan is not None:
+        sweep_reduce_shapes(args.sweep, plan, T, launch, batch, barrier, dist, dev, mk, sc, rank)
 
     e2e_ms = None
     if not args.kernel_only:
@@ -582,6 +590,32 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barr
 # (model, split, ranks) -> is the reduce inside the kernel faster than NCCL after it? Measured on B200 at
 # T=16384; a split that is not listed takes the in-kernel reduce.
 FUSED_REDUCE_WINS = {("qwen", "ep", 2): False, ("qwen", "ep", 4): False, ("qwen", "ep", 8): True}
+
+
+def sweep_reduce_shapes(spec_text, plan, T, launch, batch, barrier, dist, dev, mk, sc, rank) -> None:
+    """Times the fused launch for several (chunks, communication CTAs) shapes of the in-kernel reduce:
+    10 launches each after 3 warm-ups, max over ranks, printed on stderr."""
+    keep = (plan.chunks_by_tokens.get(T), plan.ncomm)
+    for item in spec_text.split(","):
+        c, n = (int(x) for x in item.split(":"))
+        plan.chunks_by_tokens[T], plan.ncomm = c, n
+        for _ in range(3):
+            launch(batch["hs"], batch["logits"])
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            launch(batch["hs"], batch["logits"])
+        e1.record()
+        barrier()
+        mk.check_status(sc["workspace"])
+        t = torch.tensor([e0.elapsed_time(e1) / 10], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ph = mk.workspace_view(sc["workspace"])["phase_ns"].tolist()
+        if rank == 0:
+            print(f"# reduce shape chunks={c} ncomm={n}: {float(t[0]) * 1e3:.1f} us per layer, phases "
+                  f"{[round((ph[i + 1] - ph[i]) / 1e3, 1) for i in range(4)]}", file=sys.stderr, flush=True)
+    plan.chunks_by_tokens[T], plan.ncomm = keep
 
 
 def run_sustained(seconds, ms_guess, launch, reduce_out, batch, barrier, world, dist, dev, gpu_index, flops) -> dict:

@@ -183,6 +183,31 @@ int prefill_wgmma_plan_prepare(const uint8_t* up_w_fp8, const uint8_t* down_w_fp
 void prefill_wgmma_plan_stats(unsigned long long* hits, unsigned long long* misses);
 void prefill_wgmma_plan_reset(void);
 
+/* The gated shared expert inside the same launch (in the reference it is a separate vLLM MLP whose output comes
+ * back as tp_residual, fused_moe/runner/moe_runner.py:884-906). The argument list of the _ep2 entry, then: the
+ * shared expert's block-FP8 weights in the layout of ONE routed expert (sh_up_w_fp8 e4m3 [2*N_HALF, K] gate rows then
+ * up rows, sh_up_w_scales fp32 [2*N_HALF/128, K/128], sh_down_w_fp8 e4m3 [H, N_HALF], sh_down_w_scales fp32
+ * [H/128, N_HALF/128]; under tensor parallelism the rank's slice, like the routed weights); sh_gate_bf16, bf16 [K] or
+ * null: the expert's rows are multiplied by sigmoid(x . g), by 1 when null; sh_gate_scratch fp32 [T] (required with
+ * a gate); (sh_part, sh_parts): this launch computes the shared expert for the 128-token tiles j with
+ * j % sh_parts == sh_part -- expert-parallel ranks pass (rank, world), everybody else (0, 1). output_accum has to hold
+ * num_tokens * (top_k + 1) * prefill_wgmma_partial_chunks() rows. Result: bf16(out_scale * routed + shared + residual).
+ * -108: the two-CTA build has no shared expert; -109: a shared-expert argument is null or (sh_part, sh_parts) is not
+ * a valid split; -5: descriptor encoding failed. */
+int prefill_wgmma_has_shared_expert(void);    /* 1 = launch_prefill_moe_wgmma_q1_shared is usable */
+int launch_prefill_moe_wgmma_q1_shared(const float* logits, int num_tokens, int block_m, void* workspace,
+                                       size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
+                                       float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
+                                       const uint8_t* down_w_fp8, const float* down_w_scales, float* output_accum,
+                                       int32_t* topk_ids, float* topk_weights, int32_t* sorted_token_ids,
+                                       void* bf16_output, const float* router_bias, void* tp_mc, void* tp_pads,
+                                       int tp_rank, int tp_world, int tp_nchunk, int tp_ncomm, uint32_t tp_seq,
+                                       void* tp_seqctr, const void* tp_residual, float out_scale,
+                                       const int32_t* expert_map, const uint8_t* sh_up_w_fp8,
+                                       const float* sh_up_w_scales, const uint8_t* sh_down_w_fp8,
+                                       const float* sh_down_w_scales, const void* sh_gate_bf16, float* sh_gate_scratch,
+                                       int sh_part, int sh_parts, prefill_mono_stream_t stream);
+
 int prefill_wgmma_arch(void);                 /* 100 = built for sm_100a */
 /* 1 = tiles run as pairs on clusters of two CTAs (tcgen05 cta_group::2); the total_tiles word of the
  * workspace then counts pairs, and launch_prefill_moe_wgmma_q1_gemv returns -106 (no router linear).

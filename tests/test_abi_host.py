@@ -241,13 +241,40 @@ def test_scratch_arena_grows_and_never_frees(built_libs):
     b = mk.scratch(50, "cpu")
     assert a["workspace"].data_ptr() == b["workspace"].data_ptr()
     assert a["act_fp8"].data_ptr() == b["act_fp8"].data_ptr() and b["act_fp8"].shape == (50, 2048)
-    assert b["partial"].shape == (50 * 8, 2048) and b["sorted_ids"].shape == (400,)
+    assert b["partial"].shape == (50 * 9, 2048) and b["sorted_ids"].shape == (400,)   # top_k rows + one shared-expert row
     assert mk.scratch(50, "cpu") is b                      # the views of a size are made once
     old_ptr = a["partial"].data_ptr()
     for m in (60, 70, 80, 90, 100, 30):                    # more sizes than any small cache would hold
         assert mk.scratch(m, "cpu")["partial"].data_ptr() == old_ptr
     c = mk.scratch(200, "cpu")
-    assert c["partial"].data_ptr() != old_ptr and c["partial"].shape == (1600, 2048)
+    assert c["partial"].data_ptr() != old_ptr and c["partial"].shape == (1800, 2048)
     assert len(mk._retired) == 1 and mk._retired[0]["buffers"]["partial"].data_ptr() == old_ptr
     assert mk.scratch(100, "cpu")["partial"].data_ptr() == c["partial"].data_ptr()   # later calls use the larger arena
     assert a["partial"].data_ptr() == old_ptr              # what was handed out earlier is still the same memory
+
+
+def test_shared_expert_entry_declines_bad_arguments(built_libs):
+    """launch_prefill_moe_wgmma_q1_shared: a missing shared-expert tensor, a gate without its scratch and an
+    impossible token split are refused with -109 before any CUDA call; the two-CTA build refuses with -108."""
+    vp, ci = ctypes.c_void_p, ctypes.c_int
+    buf = (ctypes.c_char * 64)()
+    p = ctypes.cast(buf, vp)
+    tail = [vp(0), vp(0), vp(0), ci(0), ci(1), ci(1), ci(0), ctypes.c_uint(0), vp(0), vp(0), ctypes.c_float(1.0), vp(0)]
+
+    def call(lib, up=p, ups=p, dn=p, dns=p, gate=vp(0), gsc=vp(0), part=0, parts=1, **kw):
+        a, keep = _args(extra=tail + [up, ups, dn, dns, gate, gsc, ci(part), ci(parts)], **kw)
+        lib.launch_prefill_moe_wgmma_q1_shared.restype = ctypes.c_int
+        return lib.launch_prefill_moe_wgmma_q1_shared(*a)
+
+    lib = MonoKernel(built_libs["qwen_w1"]).lib
+    lib.prefill_wgmma_has_shared_expert.restype = ctypes.c_int
+    assert lib.prefill_wgmma_has_shared_expert() == 1
+    assert call(lib, up=vp(0)) == -109
+    assert call(lib, dns=vp(0)) == -109
+    assert call(lib, gate=p, gsc=vp(0)) == -109
+    assert call(lib, part=4, parts=4) == -109 and call(lib, parts=0) == -109
+    assert call(lib, ws_bytes=16) == -100 and call(lib, n_tokens=0) == -101
+    pair = MonoKernel(built_libs["qwen_w1_pair"]).lib
+    pair.prefill_wgmma_has_shared_expert.restype = ctypes.c_int
+    assert pair.prefill_wgmma_has_shared_expert() == 0
+    assert call(pair) == -108

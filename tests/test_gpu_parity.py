@@ -633,3 +633,87 @@ def test_deepseek_expert_parallel_8_rank_in_sequence(gu, oracle, rank):
         gu.check_output(oracle, res["out"], gu.sample_tokens(T, 24, rank), q, s, ids, w, layer)
     del layer
     torch.cuda.empty_cache()
+
+
+def _shared_reference(oracle, toks, q, s, ids, w, layer, sh, hs, out_scale=1.0, part=(0, 1), residual=None):
+    """What the launch with the shared expert inside must produce, from the oracle's bf16 partial rows:
+    bf16(out_scale * sum_k routed_row_k + shared_row (+ residual)), all sums in fp32. The shared expert is
+    evaluated as one more expert every listed token goes to, weighted by sigmoid(x . g) (or 1 without a gate)."""
+    n = len(toks)
+    _, part_r, *_ = oracle.moe_path(toks, q, s, ids, w, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"],
+                                    want_dumps=True)
+    k = ids.shape[1]
+    owned = torch.from_numpy((ids[toks] >= 0).astype(np.float32))                      # rows of experts held elsewhere do not exist
+    routed = (part_r.float().view(n, k, -1, part_r.shape[-1]).sum(2) * owned[:, :, None]).sum(1)
+    T = ids.shape[0]
+    if sh["gate"] is not None:
+        gw = torch.sigmoid(hs.double().cpu() @ sh["gate"].double().cpu()).float().numpy().reshape(T, 1)
+    else:
+        gw = np.ones((T, 1), np.float32)
+    _, part_s, *_ = oracle.moe_path(toks, q, s, np.zeros((T, 1), np.int32), gw, sh["w13"][None], sh["w13_scale"][None],
+                                    sh["w2"][None], sh["w2_scale"][None], want_dumps=True)
+    shared = part_s.float().view(n, -1, part_s.shape[-1]).sum(1)
+    mine = torch.from_numpy(((toks // 128) % part[1] == part[0]).astype(np.float32))[:, None]
+    base = shared * mine
+    if residual is not None:
+        base = base + residual.float().cpu()[torch.from_numpy(toks).long()]
+    return (routed * out_scale + base).to(torch.bfloat16).float()
+
+
+@pytest.mark.parametrize("T", [200, 3000])
+def test_gated_shared_expert_inside_the_launch(gu, oracle, T):
+    """The sigmoid-gated shared expert of the Qwen-like layer computed by the same launch as the routed experts
+    (as dense tiles appended to the tile schedule): routing stays bit-exact, and the output equals
+    bf16(routed + sigmoid(x . g) * shared(x)) built from the oracle's partial rows. A launch without the shared
+    expert afterwards is bitwise what it was before."""
+    from unimonomoe_b200.loader import prepare_shared_expert
+    mk = gu.kernel("qwen_w1")
+    assert mk.has_shared
+    layer = synth.make_layer(synth.QWEN, seed=0, device=gu.DEV, with_shared=True)
+    shd = layer["shared"]
+    sh = prepare_shared_expert(shd["w13"], shd["w13_scale"], shd["w2"], shd["w2_scale"], shd["gate"])
+    batch = synth.make_batch(synth.QWEN, layer, T, seed=12, device=gu.DEV)
+    before = gu.launch(mk, layer, batch)
+    out = torch.full((T, 2048), float("nan"), dtype=torch.bfloat16, device=gu.DEV)
+    sc = mk.prefill_impl(batch["hs"], batch["logits"], layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], 8,
+                         True, None, out, check=True, shared=sh)
+    assert torch.isfinite(out.float()).all()
+    ids, w, _ = oracle.route(batch["logits"], mode=0)
+    assert (sc["topk_ids"].cpu().numpy() == ids).all()
+    q, s = oracle.quant_act(batch["hs"])
+    toks = gu.sample_tokens(T, 160, 6)
+    ref = _shared_reference(oracle, toks, q, s, ids, w, layer, sh, batch["hs"])
+    gu.assert_close(oracle, out.float().cpu()[torch.from_numpy(toks).long()], ref, steps=2)
+    # the shared half is really there: without it the result is far away
+    m = oracle.parity_metrics(before["out"].float().cpu()[torch.from_numpy(toks).long()], ref)
+    assert m["rel_l2"] > 0.05, m
+    after = gu.launch(mk, layer, batch)
+    assert torch.equal(after["out"].view(torch.int16), before["out"].view(torch.int16))
+
+
+def test_shared_expert_with_scale_residual_and_token_split(gu, oracle):
+    """DeepSeek-like shard (ungated shared expert, routed_scaling_factor 2.5 on the routed half, a residual) and
+    the token split used by expert-parallel ranks: a launch with (part, parts) = (1, 4) adds the shared expert
+    only for the 128-token tiles j with j % 4 == 1."""
+    from unimonomoe_b200.loader import prepare_shared_expert
+    spec, mk = synth.DEEPSEEK, gu.kernel("ds_tp8")
+    layer = synth.make_layer(spec, seed=0, device=gu.DEV, inter_slice=(0, 256), with_shared=False, chunk=8)
+    g = torch.Generator(device=gu.DEV).manual_seed(77)
+    sw13, sw13s = synth.quantize_block_fp8((torch.randn(512, 7168, device=gu.DEV, generator=g) * 0.02).to(torch.bfloat16))
+    sw2, sw2s = synth.quantize_block_fp8((torch.randn(7168, 256, device=gu.DEV, generator=g) * 0.02).to(torch.bfloat16))
+    sh = prepare_shared_expert(sw13, sw13s, sw2, sw2s, None)
+    T = 900
+    batch = synth.make_batch(spec, layer, T, seed=3, device=gu.DEV)
+    resid = (torch.randn(T, 7168, device=gu.DEV, generator=g) * 0.05).to(torch.bfloat16)
+    ids, w, _ = oracle.route(batch["logits"], mode=2, bias=layer["bias"])
+    q, s = oracle.quant_act(batch["hs"])
+    toks = gu.sample_tokens(T, 48, 8)
+    for part in ((0, 1), (1, 4)):
+        out = torch.full((T, 7168), float("nan"), dtype=torch.bfloat16, device=gu.DEV)
+        mk.prefill_impl(batch["hs"], batch["logits"], layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], 8,
+                        True, layer["bias"], out, residual=resid, out_scale=2.5, check=True, shared=sh, shared_part=part)
+        assert torch.isfinite(out.float()).all()
+        ref = _shared_reference(oracle, toks, q, s, ids, w, layer, sh, batch["hs"], out_scale=2.5, part=part, residual=resid)
+        gu.assert_close(oracle, out.float().cpu()[torch.from_numpy(toks).long()], ref, steps=2)
+    del layer
+    torch.cuda.empty_cache()

@@ -96,6 +96,18 @@ def build_variant(variant: str, force: bool = False, verbose: bool = False) -> s
     return out
 
 
+def build_microbench() -> str:
+    """The hardware micro-benchmarks of csrc/sm100_microbench.cu as an executable (development tool)."""
+    os.makedirs(LIBDIR, exist_ok=True)
+    out = os.path.join(LIBDIR, "sm100_microbench")
+    cmd = [os.environ.get("NVCC", "nvcc"), "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+           "-I", CSRC, os.path.join(CSRC, "sm100_microbench.cu"), "-o", out]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("nvcc failed for the micro-benchmarks:\n" + r.stdout + r.stderr)
+    return out
+
+
 def build_all(names=None, force: bool = False, verbose: bool = False) -> dict:
     names = list(names or VARIANTS)
     with ThreadPoolExecutor(max_workers=min(8, len(names))) as ex:
@@ -105,6 +117,11 @@ def build_all(names=None, force: bool = False, verbose: bool = False) -> dict:
 
 if __name__ == "__main__":
     sel = [a for a in sys.argv[1:] if not a.startswith("-")]
+    if "microbench" in sel:
+        print("microbench ->", build_microbench())
+        sel.remove("microbench")
+        if not sel:
+            sys.exit(0)
     res = build_all(sel or None, force="--force" in sys.argv, verbose=True)
     for k, v in res.items():
         print(k, "->", v)

@@ -242,17 +242,29 @@ struct Params {
   float* dbg_acc;
   uint8_t* dbg_inter;
   float* dbg_inter_scale;
+  // shared expert computed in the same launch (sh_on == 0: none). Its tiles are the token tiles j with
+  // j % sh_parts == sh_part; its partial rows follow the routed ones in `partial`.
+  const float* sh_up_scales;
+  const float* sh_down_scales;
+  const __nv_bfloat16* sh_gate;   // [K] gate vector (sigmoid(x . g) scales the row), or null: weight 1
+  float* sh_gate_w;               // [T] fp32, written by phase 0 when sh_gate is given
+  int sh_on, sh_part, sh_parts;
   // router GEMV (null: the caller supplied the logits)
   float* logits_out;        // [T, E] fp32, written by phase R and read back by phase 0
   alignas(64) CUtensorMap tm_up;
   alignas(64) CUtensorMap tm_down;
   alignas(64) CUtensorMap tm_x;    // bf16 activations [T, K]
   alignas(64) CUtensorMap tm_rw;   // bf16 router weight [E, K]
+  alignas(64) CUtensorMap tm_sh_up;    // shared expert [2 * N_HALF, K]
+  alignas(64) CUtensorMap tm_sh_down;  // shared expert [H, N_HALF]
 };
 
+// e == SHARED_E marks a tile of the shared expert: its rows are the tokens row0 .. row0 + rows - 1 themselves
+// (no sort indirection), its weights the shared expert's.
 struct TileInfo {
   int e, row0, rows, chunk;
 };
+constexpr int SHARED_E = E_LOCAL;
 
 // ------------------------------------------------------------------ small helpers
 __device__ __forceinline__ uint32_t float_key(float f) {
@@ -470,7 +482,9 @@ __device__ __forceinline__ void quant_token_load(const Params& p, int tok, int p
       raw[u] = *reinterpret_cast<const uint4*>(p.act_bf16 + static_cast<size_t>(tok) * K_DIM + kb * 128 + sub * 8);
   }
 }
-__device__ __forceinline__ void quant_token_store(const Params& p, int tok, int piece, int lane, const uint4 (&raw)[QU]) {
+// `gdot` collects this lane's part of x . g for the shared expert's gate (g == nullptr: nothing is added).
+__device__ __forceinline__ void quant_token_store(const Params& p, int tok, int piece, int lane, const uint4 (&raw)[QU],
+                                                  const __nv_bfloat16* g, float& gdot) {
   const int half = lane >> 4, sub = lane & 15;
 #pragma unroll
   for (int u = 0; u < QU; ++u) {
@@ -482,6 +496,12 @@ __device__ __forceinline__ void quant_token_store(const Params& p, int tok, int 
     for (int i = 0; i < 8; ++i) {
       x[i] = __bfloat162float(b[i]);
       am = fmaxf(am, fabsf(x[i]));
+    }
+    if (g != nullptr && kb < NK) {
+      const uint4 gr = __ldg(reinterpret_cast<const uint4*>(g + kb * 128 + sub * 8));
+      const __nv_bfloat16* gb = reinterpret_cast<const __nv_bfloat16*>(&gr);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) gdot = __fmaf_rn(x[i], __bfloat162float(gb[i]), gdot);
     }
 #pragma unroll
     for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, off));
@@ -723,11 +743,16 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         if (lid >= 0) hist[warp * E + lid] += 1;  // ids of one token are distinct: no conflict
       }
       __syncwarp();  // the next token's increments may hit the same counters from other lanes
-      quant_token_store(p, t + a, 0, lane, qraw[a]);
+      float gdot = 0.f;
+      quant_token_store(p, t + a, 0, lane, qraw[a], p.sh_gate, gdot);
 #pragma unroll 1
       for (int piece = 1; piece < Q_PIECES; ++piece) {
         quant_token_load(p, t + a, piece, lane, qraw[a]);
-        quant_token_store(p, t + a, piece, lane, qraw[a]);
+        quant_token_store(p, t + a, piece, lane, qraw[a], p.sh_gate, gdot);
+      }
+      if (p.sh_gate != nullptr) {   // gate of the shared expert: sigmoid(x . g), one value per token
+        gdot = warp_sum_f(gdot);
+        if (lane == 0) p.sh_gate_w[t + a] = det_sigmoidf(gdot);
       }
     }
     __syncwarp();
@@ -821,8 +846,32 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       }
     }
     __syncthreads();
+    // the shared expert's units follow the routed ones in the deal: token tile j (128 tokens), chunk fastest
+    int sh_units = 0;
+    if (p.sh_on) {
+      const int tok_tiles = (T + TILE_M - 1) / TILE_M;
+      const int mine = (tok_tiles > p.sh_part) ? (tok_tiles - p.sh_part + p.sh_parts - 1) / p.sh_parts : 0;
+      sh_units = mine * NCH;
+      const int tt_routed = S.total_tiles;
+      for (int i = tid; i < sh_units; i += BLOCK) {
+        const int g = tt_routed + i;
+        if (g % SCHED_UNITS == sched_me) {
+          const int slot = g / SCHED_UNITS;
+          if (slot < MAX_MY_TILES) {
+            TileInfo ti;
+            ti.e = SHARED_E;
+            ti.row0 = (p.sh_part + (i / NCH) * p.sh_parts) * TILE_M;
+            ti.rows = max(0, min(TILE_M, T - ti.row0));
+            ti.chunk = i % NCH;
+            S.tiles[slot] = ti;
+          } else {
+            report_error(ws, kErrBounds, 3, static_cast<uint32_t>(g), static_cast<uint32_t>(slot));
+          }
+        }
+      }
+    }
     if (tid == 0) {
-      const int tt = S.total_tiles;
+      const int tt = S.total_tiles + sh_units;
       S.n_my_tiles = (tt > sched_me) ? min(MAX_MY_TILES, (tt - sched_me + SCHED_UNITS - 1) / SCHED_UNITS) : 0;
     }
     // stable scatter: each warp re-walks its own tokens in ascending order
@@ -893,7 +942,11 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         bool ok = true;
         PROF_DECL(pw_emptyB);
         for (int it = 0; it < n_my && ok; ++it) {
-          const int e = S.tiles[it].e, ch = S.tiles[it].chunk;
+          const int ch = S.tiles[it].chunk;
+          const bool sh = S.tiles[it].e == SHARED_E;
+          const int e = sh ? 0 : S.tiles[it].e;                     // row base inside the weight tensor
+          const CUtensorMap* map_up = sh ? &p.tm_sh_up : &p.tm_up;
+          const CUtensorMap* map_down = sh ? &p.tm_sh_down : &p.tm_down;
           for (int ps = 0; ps < NP && ok; ++ps) {
             const uint32_t yg = static_cast<uint32_t>(e * N_UP + ch * CHUNK_COLS + ps * 128);
             const uint32_t yu = yg + N_HALF;
@@ -910,8 +963,8 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
                 // counted on the leader's barrier
                 if (leader) mbar_arrive_expect_tx(&S.fullB[st], 2 * B_STAGE_BYTES);
                 const uint32_t co = crank * HCB;
-                tma_load_2d_pair(&p.tm_up, x, yg + co, dst, at_leader(&S.fullB[st]));
-                tma_load_2d_pair(&p.tm_up, x, yu + co, dst + HCB * 128, at_leader(&S.fullB[st]));
+                tma_load_2d_pair(map_up, x, yg + co, dst, at_leader(&S.fullB[st]));
+                tma_load_2d_pair(map_up, x, yu + co, dst + HCB * 128, at_leader(&S.fullB[st]));
                 ++nb;
                 continue;
               }
@@ -924,8 +977,8 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
 #pragma unroll
                 for (int hh = 0; hh < EPI_WGS; ++hh) {
                   const uint32_t co = static_cast<uint32_t>(j * PASS_STRIDE + hh * HCB);
-                  tma_load_2d(&p.tm_up, x, yg + co, dst + (j * BC + hh * WC) * 128, &S.fullB[st]);
-                  tma_load_2d(&p.tm_up, x, yu + co, dst + (j * BC + hh * WC + HCB) * 128, &S.fullB[st]);
+                  tma_load_2d(map_up, x, yg + co, dst + (j * BC + hh * WC) * 128, &S.fullB[st]);
+                  tma_load_2d(map_up, x, yu + co, dst + (j * BC + hh * WC + HCB) * 128, &S.fullB[st]);
                 }
               }
               ++nb;
@@ -942,14 +995,14 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
                 if (leader) mbar_arrive_expect_tx(&S.fullB[st], 2 * B_STAGE_BYTES);
 #pragma unroll
                 for (int j = 0; j < B_ROWS / HCB; ++j)
-                  tma_load_2d_pair(&p.tm_down, x, y + crank * B_ROWS + j * HCB, dst + j * HCB * 128, at_leader(&S.fullB[st]));
+                  tma_load_2d_pair(map_down, x, y + crank * B_ROWS + j * HCB, dst + j * HCB * 128, at_leader(&S.fullB[st]));
                 ++nb;
                 continue;
               }
               mbar_arrive_expect_tx(&S.fullB[st], (MONO_ABLATE & 16) ? 0 : B_STAGE_BYTES);
               if constexpr ((MONO_ABLATE & 16) != 0) { ++nb; continue; }
 #pragma unroll
-              for (int j = 0; j < 256 / HCB; ++j) tma_load_2d(&p.tm_down, x, y + j * HCB, dst + j * HCB * 128, &S.fullB[st]);
+              for (int j = 0; j < 256 / HCB; ++j) tma_load_2d(map_down, x, y + j * HCB, dst + j * HCB * 128, &S.fullB[st]);
               ++nb;
             }
           }
@@ -1090,8 +1143,12 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
           const int r = gt + hh * 64;
           int t = -1;
           if (r < ti.rows) {
-            const int fi = __ldcg(&p.sorted_ids[ti.row0 + r]);
-            if (fi >= 0 && fi < numel) t = fi / TOP_K;
+            if (ti.e == SHARED_E) {
+              t = ti.row0 + r;                       // the shared expert takes the tokens in order
+            } else {
+              const int fi = __ldcg(&p.sorted_ids[ti.row0 + r]);
+              if (fi >= 0 && fi < numel) t = fi / TOP_K;
+            }
           }
           S.gather_tok[it & 1][r & 7][r >> 3] = t;
         }
@@ -1180,36 +1237,55 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       // global load. stage_* below fetch tile `nx`: its row's slot id, routing weight and
       // activation scales (warpgroups 0 and 1 load half a row each), and the expert's weight
       // scales (into buffer nx & 1).
-      int nfi = -1;
+      // nfi: index of the row's partial row (routed: its flat slot t * top_k + k; shared expert: numel + token);
+      // ntok: its token
+      int nfi = -1, ntok = -1;
       float nrw = 0.f, wsu_v = 0.f, wsd_v = 0.f;
       float4 as_v = make_float4(0.f, 0.f, 0.f, 0.f);
       auto stage_ids = [&](int nx) {
         const TileInfo tn = S.tiles[nx];
+        const bool sh = tn.e == SHARED_E;
         nfi = -1;
+        ntok = -1;
         if (r < tn.rows) {
-          nfi = __ldcg(&p.sorted_ids[tn.row0 + r]);
-          if (nfi < 0 || nfi >= numel) nfi = -1;
+          if (sh) {
+            ntok = tn.row0 + r;
+            nfi = numel + ntok;
+          } else {
+            nfi = __ldcg(&p.sorted_ids[tn.row0 + r]);
+            if (nfi < 0 || nfi >= numel) nfi = -1;
+            else ntok = nfi / TOP_K;
+          }
         }
-        if (et < WSU_N) wsu_v = __ldg(p.up_w_scales + wsu_index(tn.e, tn.chunk, et));
-        if (et < WSD_N) wsd_v = __ldg(p.down_w_scales + wsd_index(tn.e, tn.chunk, et));
+        const float* su = sh ? p.sh_up_scales : p.up_w_scales;
+        const float* sd = sh ? p.sh_down_scales : p.down_w_scales;
+        const int es = sh ? 0 : tn.e;
+        if (et < WSU_N) wsu_v = __ldg(su + wsu_index(es, tn.chunk, et));
+        if (et < WSD_N) wsd_v = __ldg(sd + wsd_index(es, tn.chunk, et));
       };
       auto stage_weight_store = [&](int nx) {
-        nrw = (nfi >= 0) ? __ldcg(&p.topk_weights[nfi]) : 0.f;
+        const bool sh = S.tiles[nx].e == SHARED_E;
+        if (nfi < 0) nrw = 0.f;
+        else if (!sh) nrw = __ldcg(&p.topk_weights[nfi]);
+        else nrw = (p.sh_gate != nullptr) ? __ldcg(&p.sh_gate_w[ntok]) : 1.f;
         if (et < WSU_N) wsu_sm[(nx & 1) * WSU_N + et] = wsu_v;
         if (et < WSD_N) wsd_sm[(nx & 1) * WSD_N + et] = wsd_v;
+        const float* su = sh ? p.sh_up_scales : p.up_w_scales;
+        const float* sd = sh ? p.sh_down_scales : p.down_w_scales;
+        const int es = sh ? 0 : S.tiles[nx].e;
         if constexpr (WSU_N > N_EPI) {
           for (int i = et + N_EPI; i < WSU_N; i += N_EPI)
-            wsu_sm[(nx & 1) * WSU_N + i] = __ldg(p.up_w_scales + wsu_index(S.tiles[nx].e, S.tiles[nx].chunk, i));
+            wsu_sm[(nx & 1) * WSU_N + i] = __ldg(su + wsu_index(es, S.tiles[nx].chunk, i));
         }
         if constexpr (WSD_N > N_EPI) {
           for (int i = et + N_EPI; i < WSD_N; i += N_EPI)
-            wsd_sm[(nx & 1) * WSD_N + i] = __ldg(p.down_w_scales + wsd_index(S.tiles[nx].e, S.tiles[nx].chunk, i));
+            wsd_sm[(nx & 1) * WSD_N + i] = __ldg(sd + wsd_index(es, S.tiles[nx].chunk, i));
         }
       };
       auto as_piece_load = [&](int j) {
         as_v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (h < 2 && nfi >= 0)
-          as_v = __ldcg(reinterpret_cast<const float4*>(p.act_scales + static_cast<size_t>(nfi / TOP_K) * NK + h * (NK / 2) + 4 * j));
+          as_v = __ldcg(reinterpret_cast<const float4*>(p.act_scales + static_cast<size_t>(ntok) * NK + h * (NK / 2) + 4 * j));
       };
       auto as_piece_store = [&](int j) {
         if (h < 2) {
@@ -1258,7 +1334,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             }
           }
           PROF_T0();
-          if (p.dbg_acc != nullptr && fi >= 0 && !dead) {
+          if (p.dbg_acc != nullptr && fi >= 0 && !dead && ti.e != SHARED_E) {
             float* d = p.dbg_acc + static_cast<size_t>(ti.row0 + r) * N_UP;
 #pragma unroll
             for (int j = 0; j < NSPLIT; ++j) {
@@ -1313,11 +1389,11 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               qv.w = pack_e4m3x4(a[6].x * inv, a[6].y * inv, a[7].x * inv, a[7].y * inv);
               const int col0 = j * PASS_STRIDE + h * HCB + c * 16;  // column inside the pass's 128
               *reinterpret_cast<uint4*>(irow + sw128(r, col0 / 16)) = qv;
-              if (p.dbg_inter != nullptr && fi >= 0 && !dead)
+              if (p.dbg_inter != nullptr && fi >= 0 && !dead && ti.e != SHARED_E)
                 *reinterpret_cast<uint4*>(p.dbg_inter + static_cast<size_t>(ti.row0 + r) * N_HALF + ti.chunk * CHUNK_COLS + ps * 128 + col0) = qv;
             }
           }
-          if (p.dbg_inter_scale != nullptr && fi >= 0 && h == 0 && !dead)
+          if (p.dbg_inter_scale != nullptr && fi >= 0 && h == 0 && !dead && ti.e != SHARED_E)
             p.dbg_inter_scale[static_cast<size_t>(ti.row0 + r) * NPT + ti.chunk * NP + ps] = my_scale;
           // publish this pass's 128 intermediate columns to the tensor core (async proxy)
           fence_proxy_async_smem();
@@ -1470,7 +1546,30 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             for (int i = 0; i < W; ++i) s[i] += __bfloat162float(b[i]);
           }
           __nv_bfloat16 o[W];
-          if (p.residual != nullptr) {
+          if (p.sh_on) {
+            // out = bf16(routed * out_scale + (shared expert's rows, already times its gate) + residual)
+            float base[W];
+#pragma unroll
+            for (int i = 0; i < W; ++i) base[i] = 0.f;
+            if (static_cast<int>(tok / TILE_M) % p.sh_parts == p.sh_part) {   // rows this launch computed
+#pragma unroll
+              for (int c = 0; c < NCH; ++c) {
+                const uint4 sr = __ldcg(reinterpret_cast<const uint4*>(
+                    p.partial + ((static_cast<size_t>(numel) + tok) * NCH + c) * H_DIM + hv * W));
+                const __nv_bfloat16* sb = reinterpret_cast<const __nv_bfloat16*>(&sr);
+#pragma unroll
+                for (int i = 0; i < W; ++i) base[i] += __bfloat162float(sb[i]);
+              }
+            }
+            if (p.residual != nullptr) {
+              const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + iv * W);
+              const __nv_bfloat16* rb = reinterpret_cast<const __nv_bfloat16*>(&rr);
+#pragma unroll
+              for (int i = 0; i < W; ++i) base[i] += __bfloat162float(rb[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < W; ++i) o[i] = __float2bfloat16(__fmaf_rn(s[i], p.out_scale, base[i]));
+          } else if (p.residual != nullptr) {
             const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + iv * W);
             const __nv_bfloat16* rb = reinterpret_cast<const __nv_bfloat16*>(&rr);
 #pragma unroll
@@ -1766,6 +1865,17 @@ void prefill_wgmma_plan_reset() {
   g_maps.clear();
 }
 
+// The shared expert of a launch (all null / zero: none).
+struct SharedExpertArgs {
+  const uint8_t* up_w_fp8;      // e4m3 [2 * N_HALF, K], gate rows then up rows
+  const float* up_w_scales;     // fp32 [2 * N_HALF / 128, K / 128]
+  const uint8_t* down_w_fp8;    // e4m3 [H, N_HALF]
+  const float* down_w_scales;   // fp32 [H / 128, N_HALF / 128]
+  const void* gate_bf16;        // bf16 [K] or null
+  float* gate_scratch;          // fp32 [T], required with gate_bf16
+  int part, parts;
+};
+
 // Common launcher. router_w == nullptr: `logits` holds the caller's router logits. Otherwise
 // router_w is the bf16 router weight [E, K] and `logits` is the [T, E] fp32 buffer the kernel fills.
 static int launch_common(const void* router_w, float* logits_buf, const float* logits, int num_tokens, int block_m,
@@ -1777,9 +1887,11 @@ static int launch_common(const void* router_w, float* logits_buf, const float* l
                                     void* bf16_output, const float* router_bias, void* tp_mc, void* tp_pads,
                                     int tp_rank, int tp_world, int tp_nchunk, int tp_ncomm, uint32_t tp_seq,
                                     void* tp_seqctr, const void* tp_residual, float out_scale,
-                                    const int32_t* expert_map, cudaStream_t stream) {
+                                    const int32_t* expert_map, cudaStream_t stream,
+                                    const SharedExpertArgs* sh = nullptr) {
   (void)block_m;  // the tile height is the compiled TILE_M
   if (router_w != nullptr && PAIR) return -106;  // the pair build has no router linear
+  if (sh != nullptr && PAIR) return -108;        // nor the shared expert
   if (router_w != nullptr) logits = logits_buf;
   // order of the checks as in kernel/qwen_ep/src/prefill_mono_final_nb.cu:1650-1660
   if (workspace == nullptr || workspace_bytes < sizeof(Workspace)) return -100;
@@ -1787,12 +1899,19 @@ static int launch_common(const void* router_w, float* logits_buf, const float* l
   if (!EP_BUILD && expert_map != nullptr) return -121;
   if (num_tokens <= 0) return -101;
   const long long numel = static_cast<long long>(num_tokens) * TOP_K;
-  if ((numel / TILE_M + E_LOCAL) * NCH > MAX_TILES) return -102;
+  const long long sh_tiles = (sh != nullptr) ? (num_tokens + TILE_M - 1) / TILE_M : 0;
+  if ((numel / TILE_M + E_LOCAL + sh_tiles) * NCH > MAX_TILES) return -102;
   if (logits == nullptr || act_bf16 == nullptr || act_fp8 == nullptr || act_scales == nullptr ||
       up_w_fp8 == nullptr || up_w_scales == nullptr || down_w_fp8 == nullptr || down_w_scales == nullptr ||
       output_accum == nullptr || topk_ids == nullptr || topk_weights == nullptr || sorted_token_ids == nullptr ||
       bf16_output == nullptr)
     return -104;
+  if (sh != nullptr) {
+    if (sh->up_w_fp8 == nullptr || sh->up_w_scales == nullptr || sh->down_w_fp8 == nullptr ||
+        sh->down_w_scales == nullptr || (sh->gate_bf16 != nullptr && sh->gate_scratch == nullptr))
+      return -109;
+    if (sh->parts < 1 || sh->part < 0 || sh->part >= sh->parts) return -109;
+  }
   if (tp_mc != nullptr && tp_ncomm > 0) {
     if (tp_nchunk < 1 || tp_nchunk > kTpMaxChunks) return -110;
     if (tp_ncomm >= kGrid) return -111;
@@ -1849,6 +1968,23 @@ static int launch_common(const void* router_w, float* logits_buf, const float* l
   if (rc != 0) {
     fprintf(stderr, "down-projection tensor map failed: %d\n", rc);
     return -3;
+  }
+  if (sh != nullptr) {
+    p.sh_on = 1;
+    p.sh_up_scales = sh->up_w_scales;
+    p.sh_down_scales = sh->down_w_scales;
+    p.sh_gate = static_cast<const __nv_bfloat16*>(sh->gate_bf16);
+    p.sh_gate_w = sh->gate_scratch;
+    p.sh_part = sh->part;
+    p.sh_parts = sh->parts;
+    rc = cached_map(&p.tm_sh_up, 0, sh->up_w_fp8, static_cast<uint64_t>(N_UP), K_DIM, HCB);
+    if (rc == 0) rc = cached_map(&p.tm_sh_down, 1, sh->down_w_fp8, static_cast<uint64_t>(H_DIM), N_HALF, HCB);
+    if (rc != 0) {
+      fprintf(stderr, "shared-expert tensor map failed: %d\n", rc);
+      return -5;
+    }
+  } else {
+    p.sh_parts = 1;
   }
   if (router_w != nullptr) {
     p.logits_out = logits_buf;
@@ -1940,6 +2076,34 @@ int launch_prefill_moe_wgmma_q1_gemv(const void* router_w_bf16, float* logits_ou
                        act_fp8, act_scales, up_w_fp8, up_w_scales, down_w_fp8, down_w_scales, output_accum, topk_ids,
                        topk_weights, sorted_token_ids, bf16_output, router_bias, tp_mc, tp_pads, tp_rank, tp_world,
                        tp_nchunk, tp_ncomm, tp_seq, tp_seqctr, tp_residual, out_scale, expert_map, stream);
+}
+
+// The gated shared expert inside the same launch. The argument list of the _ep2 entry, then the shared
+// expert: block-FP8 weights in the layout of one routed expert ([2 * N_HALF, K] and [H, N_HALF] with their
+// [128,128] scales), an optional bf16 gate vector [K] (the row is multiplied by sigmoid(x . g); null: by 1) with
+// its [T] fp32 scratch, and (sh_part, sh_parts): this launch computes the shared expert for the 128-token tiles
+// j with j % sh_parts == sh_part (expert-parallel ranks split the tokens; 0, 1 otherwise). output_accum has to
+// hold num_tokens * (top_k + 1) * partial_chunks rows. out = bf16(out_scale * routed + shared + residual).
+// -108: not in the two-CTA build; -109: a shared-expert argument is missing or inconsistent; -5: descriptor.
+int prefill_wgmma_has_shared_expert() { return PAIR ? 0 : 1; }
+int launch_prefill_moe_wgmma_q1_shared(const float* logits, int num_tokens, int block_m, void* workspace,
+                                       size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
+                                       float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
+                                       const uint8_t* down_w_fp8, const float* down_w_scales, float* output_accum,
+                                       int32_t* topk_ids, float* topk_weights, int32_t* sorted_token_ids,
+                                       void* bf16_output, const float* router_bias, void* tp_mc, void* tp_pads,
+                                       int tp_rank, int tp_world, int tp_nchunk, int tp_ncomm, uint32_t tp_seq,
+                                       void* tp_seqctr, const void* tp_residual, float out_scale,
+                                       const int32_t* expert_map, const uint8_t* sh_up_w_fp8,
+                                       const float* sh_up_w_scales, const uint8_t* sh_down_w_fp8,
+                                       const float* sh_down_w_scales, const void* sh_gate_bf16, float* sh_gate_scratch,
+                                       int sh_part, int sh_parts, cudaStream_t stream) {
+  const SharedExpertArgs sh{sh_up_w_fp8, sh_up_w_scales, sh_down_w_fp8, sh_down_w_scales, sh_gate_bf16,
+                            sh_gate_scratch, sh_part, sh_parts};
+  return launch_common(nullptr, nullptr, logits, num_tokens, block_m, workspace, workspace_bytes, act_bf16, act_fp8,
+                       act_scales, up_w_fp8, up_w_scales, down_w_fp8, down_w_scales, output_accum, topk_ids,
+                       topk_weights, sorted_token_ids, bf16_output, router_bias, tp_mc, tp_pads, tp_rank, tp_world,
+                       tp_nchunk, tp_ncomm, tp_seq, tp_seqctr, tp_residual, out_scale, expert_map, stream, &sh);
 }
 
 int launch_prefill_moe_wgmma_q1_tp2(const float* logits, int num_tokens, int block_m, void* workspace,

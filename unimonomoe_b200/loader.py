@@ -57,6 +57,17 @@ def prepare_router_weight(weight: torch.Tensor) -> torch.Tensor:
     return w16
 
 
+def prepare_shared_expert(w13, w13_scale, w2, w2_scale, gate=None) -> dict:
+    """The shared expert as the launch wants it, converted once at load time: block-FP8 weights in the layout
+    of one routed expert (w13 [2*I, K] gate rows then up rows, w2 [H, I], one fp32 scale per [128,128] block)
+    and, for a gated shared expert, the gate vector as contiguous bfloat16 [K]."""
+    sh = {"w13": w13.contiguous().view(torch.uint8), "w13_scale": w13_scale.float().contiguous(),
+          "w2": w2.contiguous().view(torch.uint8), "w2_scale": w2_scale.float().contiguous(), "gate": None}
+    if gate is not None:
+        sh["gate"] = gate.reshape(-1).to(torch.bfloat16).contiguous()
+    return sh
+
+
 class MonoKernel:
     """One loaded ``libprefill_mono_*.so``."""
 
@@ -78,6 +89,7 @@ class MonoKernel:
         self.has_tp2 = self._bind("launch_prefill_moe_wgmma_q1_tp2")
         self.has_ep = self._bind("launch_prefill_moe_wgmma_q1_ep")
         self.has_gemv = self._bind("launch_prefill_moe_wgmma_q1_gemv") and bool(self._int_symbol("has_router_gemv"))
+        self.has_shared = self._bind("launch_prefill_moe_wgmma_q1_shared") and bool(self._int_symbol("has_shared_expert"))
         self._caps = {}
         for name in _TP_CAP_SYMBOLS:
             self._caps[name] = self._int_symbol(name)
@@ -204,7 +216,9 @@ class MonoKernel:
             "topk_ids": torch.empty(tokens, k, dtype=torch.int32, device=device),
             "topk_weights": torch.empty(tokens, k, dtype=torch.float32, device=device),
             "sorted_ids": torch.empty(tokens * k, dtype=torch.int32, device=device),
-            "partial": torch.empty(tokens * k * chunks, H, dtype=torch.bfloat16, device=device),
+            # top_k rows per token for the routed experts plus one for a shared expert computed in the launch
+            "partial": torch.empty(tokens * (k + 1) * chunks, H, dtype=torch.bfloat16, device=device),
+            "shared_gate": torch.empty(tokens, dtype=torch.float32, device=device),
         }
 
     def scratch(self, M: int, device) -> dict:
@@ -236,7 +250,8 @@ class MonoKernel:
             chunks = self._int_symbol("partial_chunks") or 1
             sc = {"workspace": buf["workspace"], "act_fp8": buf["act_fp8"][:M], "act_scales": buf["act_scales"][:M],
                   "topk_ids": buf["topk_ids"][:M], "topk_weights": buf["topk_weights"][:M],
-                  "sorted_ids": buf["sorted_ids"][:M * k], "partial": buf["partial"][:M * k * chunks]}
+                  "sorted_ids": buf["sorted_ids"][:M * k], "partial": buf["partial"][:M * (k + 1) * chunks],
+                  "shared_gate": buf["shared_gate"][:M]}
             arena["views"][M] = sc
         return sc
 
@@ -266,13 +281,18 @@ class MonoKernel:
     # ------------------------------------------------------------------ launch
     def prefill_impl(self, activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
                      expert_scales_down, top_k, renormalize, e_score_correction_bias, out, tp=None, residual=None,
-                     out_scale=1.0, expert_map=None, scratch=None, check=False, router_weight=None) -> dict:
+                     out_scale=1.0, expert_map=None, scratch=None, check=False, router_weight=None, shared=None,
+                     shared_part=(0, 1)) -> dict:
         """Launch the kernel into ``out`` (_custom_ops.py:4568-4762). Returns the scratch dict
         (topk_ids, topk_weights, sorted_ids, workspace, ...) the launch wrote.
 
         With ``router_weight`` (the gate weight [E, K] in bf16, see `prepare_router_weight`) the router
         linear runs inside the launch; ``router_logits`` is then ignored and may be None, and the logits
-        the kernel routed on are left in ``scratch["logits"]``."""
+        the kernel routed on are left in ``scratch["logits"]``.
+
+        With ``shared`` (see `prepare_shared_expert`) the gated shared expert is computed in the same launch:
+        out = bf16(out_scale * routed + shared (+ residual)). ``shared_part = (r, n)`` restricts it to the
+        128-token tiles j with j % n == r, so that expert-parallel ranks split the tokens between them."""
         if not torch.cuda.is_available() or not activations_in.is_cuda:
             raise RuntimeError("the FP8 MoE prefill kernel needs a CUDA device; there is no CPU path")
         M, K = activations_in.shape
@@ -317,6 +337,22 @@ class MonoKernel:
         if not out.is_contiguous():
             raise RuntimeError("monokernel destination must be contiguous")
 
+        if shared is not None:
+            if not self.has_shared:
+                raise RuntimeError("loaded monokernel .so has no launch_prefill_moe_wgmma_q1_shared")
+            if router_weight is not None:
+                raise RuntimeError("the shared expert and the in-kernel router linear have separate entry points; "
+                                   "pass logits when a shared expert is given")
+            n_half = expert_weights_down.size(2)
+            want = {"w13": (2 * n_half, K), "w13_scale": (2 * n_half // 128, K // 128), "w2": (H, n_half),
+                    "w2_scale": (H // 128, n_half // 128)}
+            for name, shape in want.items():
+                if tuple(shared[name].shape) != shape or shared[name].device != device or not shared[name].is_contiguous():
+                    raise RuntimeError(f"shared expert {name} must be contiguous {shape} on {device}, got "
+                                       f"{tuple(shared[name].shape)} on {shared[name].device}")
+            g = shared.get("gate")
+            if g is not None and (g.dtype != torch.bfloat16 or tuple(g.shape) != (K,) or not g.is_contiguous()):
+                raise RuntimeError(f"shared expert gate must be contiguous bfloat16 [{K}]; use prepare_shared_expert")
         resid_ptr = 0
         if residual is not None:
             if residual.shape != (M, H) or residual.dtype != torch.bfloat16:
@@ -324,11 +360,14 @@ class MonoKernel:
                                    f"{tuple(residual.shape)} {residual.dtype}")
             if not residual.is_contiguous():
                 raise RuntimeError("monokernel folded residual must be contiguous")
-            if tp is None:
+            if tp is None and shared is None:
                 raise RuntimeError("a folded residual is only carried by the fused collective; without a TP "
                                    "configuration there is nothing to fold it into")
             resid_ptr = residual.data_ptr()
         fold = resid_ptr != 0 or float(out_scale) != 1.0
+        if fold and tp is None and shared is None:
+            raise RuntimeError("an output scale is only applied by the fused collective or together with a shared "
+                               "expert; scale the result yourself")
         if fold and not self.has_tp2:
             raise RuntimeError("loaded monokernel .so has no launch_prefill_moe_wgmma_q1_tp2, so it cannot fold a "
                                "residual or apply an output scale")
@@ -353,7 +392,17 @@ class MonoKernel:
             vp(sc["sorted_ids"].data_ptr()), vp(out.data_ptr()),
         ]
         bias_arg = vp(bias.data_ptr() if bias is not None else 0)
-        if rw is not None:
+        if shared is not None:
+            mc, pads, seqctr, rank, world, nchunk, ncomm = tp if tp is not None else (0, 0, 0, 0, 1, 1, 0)
+            entry = self.lib.launch_prefill_moe_wgmma_q1_shared
+            g = shared.get("gate")
+            args += [bias_arg, vp(int(mc)), vp(int(pads)), ctypes.c_int(int(rank)), ctypes.c_int(int(world)),
+                     ctypes.c_int(int(nchunk)), ctypes.c_int(int(ncomm)), ctypes.c_uint(0), vp(int(seqctr)),
+                     vp(int(resid_ptr)), ctypes.c_float(float(out_scale)), vp(emap.data_ptr() if emap is not None else 0),
+                     vp(shared["w13"].data_ptr()), vp(shared["w13_scale"].data_ptr()), vp(shared["w2"].data_ptr()),
+                     vp(shared["w2_scale"].data_ptr()), vp(g.data_ptr() if g is not None else 0),
+                     vp(sc["shared_gate"].data_ptr()), ctypes.c_int(int(shared_part[0])), ctypes.c_int(int(shared_part[1]))]
+        elif rw is not None:
             # one entry point carries every option: absent ones are passed as null / neutral values
             mc, pads, seqctr, rank, world, nchunk, ncomm = tp if tp is not None else (0, 0, 0, 0, 1, 1, 0)
             entry = self.lib.launch_prefill_moe_wgmma_q1_gemv
@@ -388,26 +437,28 @@ class MonoKernel:
         if rc != 0:
             raise RuntimeError(f"launch_prefill_moe_wgmma_q1 failed: rc={rc}")
         # keep the converted inputs alive until the stream has consumed them
-        sc["_keepalive"] = (act, logits, rw, w_up, w_down, s_up, s_down, bias, emap)
+        sc["_keepalive"] = (act, logits, rw, w_up, w_down, s_up, s_down, bias, emap, shared)
         if check:
             self.check_status(sc["workspace"])
         return sc
 
     def prefill(self, activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
                 expert_scales_down, top_k=8, renormalize=True, e_score_correction_bias=None, expert_map=None,
-                check=False, router_weight=None) -> torch.Tensor:
-        """Allocating variant (_custom_ops.py:4820-4858). Under EP the result is this rank's partial sum."""
+                check=False, router_weight=None, shared=None, shared_part=(0, 1), out_scale=1.0) -> torch.Tensor:
+        """Allocating variant (_custom_ops.py:4820-4858). Under EP the result is this rank's partial sum.
+        ``shared`` adds the shared expert inside the launch (``out_scale`` then scales the routed half)."""
         M, H = activations_in.size(0), expert_weights_down.size(1)
         out = torch.empty(M, H, dtype=torch.bfloat16, device=activations_in.device)
         self.prefill_impl(activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
-                          expert_scales_down, top_k, renormalize, e_score_correction_bias, out, None, None, 1.0,
-                          expert_map, check=check, router_weight=router_weight)
+                          expert_scales_down, top_k, renormalize, e_score_correction_bias, out, None, None, out_scale,
+                          expert_map, check=check, router_weight=router_weight, shared=shared, shared_part=shared_part)
         return out
 
     def prefill_out(self, activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
                     expert_scales_down, out, top_k=8, renormalize=True, e_score_correction_bias=None, tp_mc_ptr=0,
                     tp_pads_ptr=0, tp_seqctr_ptr=0, tp_rank=0, tp_world=1, tp_nchunk=0, tp_ncomm=0, tp_residual=None,
-                    tp_out_scale=1.0, check=False, expert_map=None, router_weight=None) -> None:
+                    tp_out_scale=1.0, check=False, expert_map=None, router_weight=None, shared=None,
+                    shared_part=(0, 1)) -> None:
         """Write into a caller-supplied destination (_custom_ops.py:4861-4924). tp_ncomm > 0 selects the
         fused collective, in which case ``out`` must be the symmetric window tp_mc_ptr aliases."""
         tp = None
@@ -417,7 +468,8 @@ class MonoKernel:
             tp = (tp_mc_ptr, tp_pads_ptr, tp_seqctr_ptr, tp_rank, tp_world, tp_nchunk, tp_ncomm)
         self.prefill_impl(activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
                           expert_scales_down, top_k, renormalize, e_score_correction_bias, out, tp, tp_residual,
-                          tp_out_scale, expert_map, check=check, router_weight=router_weight)
+                          tp_out_scale, expert_map, check=check, router_weight=router_weight, shared=shared,
+                          shared_part=shared_part)
 
 
 # ---------------------------------------------------------------------- module-level mirror
