@@ -402,6 +402,10 @@ def main() -> None:
                                   physical_gpu_index(local), flops)
         mk.check_status(sc["workspace"])
 
+    with_shared = None
+    if world == 1 and args.model == "qwen" and not args.kernel_only and args.variant is None and mk.has_shared:
+        with_shared = time_with_shared_expert(spec, mk, layer, batch, out, sc, args.steps, dev, flops)
+
     if args.sweep and plan is not None:
         sweep_reduce_shapes(args.sweep, plan, T, launch, batch, barrier, dist, dev, mk, sc, rank)
 
@@ -421,7 +425,7 @@ def main() -> None:
         phases = [round((ph[i + 1] - ph[i]) / 1e3, 1) for i in range(4)]
         stall_counters(mk, sc["workspace"])
         report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
-               reduce_desc, phases, sustained, parity)
+               reduce_desc, phases, sustained, parity, with_shared)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -618,6 +622,33 @@ def sweep_reduce_shapes(spec_text, plan, T, launch, batch, barrier, dist, dev, m
     plan.chunks_by_tokens[T], plan.ncomm = keep
 
 
+def time_with_shared_expert(spec, mk, layer, batch, out, sc, steps, dev, routed_flops) -> dict:
+    """Beside the contract's figure (routed experts only): the same launch with the layer's sigmoid-gated
+    shared expert computed inside it (I_sh = 512: +12.5 % FLOPs)."""
+    from unimonomoe_b200.loader import prepare_shared_expert
+    full = synth.make_layer(spec, seed=0, device="cpu", with_shared=True, expert_slice=(0, 8))["shared"]
+    sh = prepare_shared_expert(*(full[k].to(dev) for k in ("w13", "w13_scale", "w2", "w2_scale")), full["gate"].to(dev))
+
+    def go():
+        mk.prefill_impl(batch["hs"], batch["logits"], layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"],
+                        spec.top_k, True, layer["bias"], out, scratch=sc, shared=sh)
+    for _ in range(3):
+        go()
+    torch.cuda.synchronize()
+    mk.check_status(sc["workspace"])
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        go()
+    e1.record()
+    torch.cuda.synchronize()
+    mk.check_status(sc["workspace"])
+    ms = e0.elapsed_time(e1) / steps
+    T = batch["hs"].shape[0]
+    fl = routed_flops + 6.0 * T * spec.hidden * spec.shared_inter
+    return {"us_per_layer": ms * 1e3, "tflops_routed_plus_shared": fl / (ms * 1e-3) / 1e12, "flops": fl}
+
+
 def run_sustained(seconds, ms_guess, launch, reduce_out, batch, barrier, world, dist, dev, gpu_index, flops) -> dict:
     """The same launch repeated for `seconds`: the steady-state figure under the power cap, with the clocks
     seen. Nothing here touches a clock; time x median SM MHz is the clock-normalised cost."""
@@ -717,7 +748,7 @@ def verify_reduced_output(spec, mk, layer, batch, emap, sc, pool_plan, result, w
 
 
 def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
-           reduce_desc, phases=None, sustained=None, parity=None) -> None:
+           reduce_desc, phases=None, sustained=None, parity=None, with_shared=None) -> None:
     peaks = measured_peaks()
     fp8_lib = fp8_gemm_tflops(dev) if (world == 1 and not args.kernel_only) else None
     if peaks.get("bf16_tflops"):
@@ -767,6 +798,8 @@ def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flop
         sustained["frac_of_2x_bf16_sustained"] = (flops / world) / (sustained["ms_per_step"] * 1e-3) / 1e12 / sus_peak
         sustained["peak_2x_bf16_sustained"] = sus_peak
         line["sustained"] = sustained
+    if with_shared is not None:
+        line["with_shared_expert"] = with_shared
     if world > 1:
         line["parity_checked"] = bool(parity is not None and parity["ok"])
         line["parity"] = parity
