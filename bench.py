@@ -578,6 +578,27 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barr
     serial_ms = timed(serial_step, n_e2e, False)
     timed(piped_step, 4, True)
     piped_ms = timed(piped_step, n_e2e, True)
+    # where a pipelined step's time can go: host time to enqueue one step (Python, ctypes, NCCL enqueue), and the
+    # copies alone; the kernel and the all-gather alone are reported beside them
+    t0 = time.perf_counter()
+    for i in range(8):
+        piped_step(i)
+    host_enqueue_ms = (time.perf_counter() - t0) / 8 * 1e3
+    for st in (s_in, s_c, s_out):
+        cur.wait_stream(st)
+    barrier()
+
+    def alone(fn, n=5):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        barrier()
+        return a.elapsed_time(b) / n
+    account = {"host_enqueue_ms_per_step": host_enqueue_ms, "h2d_alone_ms": alone(lambda: upload(0)),
+               "d2h_alone_ms": alone(lambda: out_host[0].copy_(outs[0][rows], non_blocking=True))}
     gather_ms = 0.0
     if world > 1:   # the all-gather alone, for the record
         g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -588,7 +609,7 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barr
         g1.record()
         barrier()
         gather_ms = g0.elapsed_time(g1) / 5
-    return piped_ms, serial_ms, gather_ms, gather_kind
+    return piped_ms, serial_ms, gather_ms, gather_kind, account
 
 
 # (model, split, ranks) -> is the reduce inside the kernel faster than NCCL after it? Measured on B200 at
@@ -783,7 +804,7 @@ def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flop
                              + ("" if world == 1 else f"; each rank moves 1/{world} of the rows over PCIe and an "
                                 "all-gather over NVLink completes the inputs on every GPU"),
                  "serial_ms_per_step": e2e_ms[1], "serial_value": flops / (e2e_ms[1] * 1e-3) / 1e12,
-                 "allgather_ms": e2e_ms[2], "allgather": e2e_ms[3]}),
+                 "allgather_ms": e2e_ms[2], "allgather": e2e_ms[3], "account": e2e_ms[4]}),
         "gpu_launches": args.steps,
         "kernel_ms": kern_ms,
         # the last launch on rank 0, from the kernel's own %globaltimer stamps: routing + quantisation,

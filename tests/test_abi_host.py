@@ -278,3 +278,30 @@ def test_shared_expert_entry_declines_bad_arguments(built_libs):
     pair.prefill_wgmma_has_shared_expert.restype = ctypes.c_int
     assert pair.prefill_wgmma_has_shared_expert() == 0
     assert call(pair) == -108
+
+
+def _reference_checkout():
+    """A checkout of the reference repository, when one is at hand: $REFERENCE_CHECKOUT, or a directory named
+    `reference` beside this repository. Only CPU tests in the build container use it."""
+    cand = os.environ.get("REFERENCE_CHECKOUT") or os.path.join(os.path.dirname(ROOT), "reference")
+    return cand if os.path.isfile(os.path.join(cand, "validation", "geo_readback.py")) else None
+
+
+@pytest.mark.skipif(_reference_checkout() is None, reason="no checkout of the reference at hand")
+def test_the_references_own_readback_script_accepts_every_binary(built_libs):
+    """validation/geo_readback.py of the reference, unmodified, run against each binary built here: every
+    accessor it asks for is present and reports this build's geometry, and both expert-parallel entry points exist."""
+    import subprocess
+    import sys
+    script = os.path.join(_reference_checkout(), "validation", "geo_readback.py")
+    for variant, path in built_libs.items():
+        r = subprocess.run([sys.executable, script, path], capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0, (variant, r.stderr[-500:])
+        assert "ABSENT" not in r.stdout, (variant, r.stdout)
+        got = dict(line.split()[:2] for line in r.stdout.splitlines()[1:] if len(line.split()) >= 2)
+        g = build.VARIANTS[variant]
+        assert int(got["k_dim"]) == g["K"] and int(got["h_dim"]) == g["H"] and int(got["n_half"]) == g["N_HALF"]
+        assert int(got["num_experts_local"]) == g["E_LOCAL"] and int(got["router_mode"]) == g["MODE"]
+        assert int(got["grid_size"]) == 148 and int(got["tp_has_residual"]) == 1 and int(got["tp_has_devseq"]) == 1
+        assert got["q1_ep"] == "present" and got["q1_ep2"] == "present"
+        assert int(got["workspace_bytes"]) == MonoKernel(path).geometry()["workspace_bytes"]
