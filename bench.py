@@ -406,6 +406,13 @@ def main() -> None:
     if world == 1 and args.model == "qwen" and not args.kernel_only and args.variant is None and mk.has_shared:
         with_shared = time_with_shared_expert(spec, mk, layer, batch, out, sc, args.steps, dev, flops)
 
+    extra = None
+    if world in (4, 8) and args.model == "qwen" and args.parallel == "auto" and not args.kernel_only:
+        # the north star's other splits, each behind the same parity check: Qwen tensor parallel over 4 GPUs,
+        # the DeepSeek-V3-like layer tensor parallel over 8
+        extra = time_other_split("qwen" if world == 4 else "deepseek", world, rank, dist, dev, barrier,
+                                 8192 if world == 8 else T)
+
     if args.sweep and plan is not None:
         sweep_reduce_shapes(args.sweep, plan, T, launch, batch, barrier, dist, dev, mk, sc, rank)
 
@@ -425,7 +432,7 @@ def main() -> None:
         phases = [round((ph[i + 1] - ph[i]) / 1e3, 1) for i in range(4)]
         stall_counters(mk, sc["workspace"])
         report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
-               reduce_desc, phases, sustained, parity, with_shared)
+               reduce_desc, phases, sustained, parity, with_shared, extra)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -643,6 +650,49 @@ def sweep_reduce_shapes(spec_text, plan, T, launch, batch, barrier, dist, dev, m
     plan.chunks_by_tokens[T], plan.ncomm = keep
 
 
+def time_other_split(model, world, rank, dist, dev, barrier, T, steps=10) -> dict:
+    """One more configuration timed in the same process after the contract's own: the tensor-parallel split of
+    the Qwen-like layer (4 GPUs) or of the DeepSeek-V3-like layer (8 GPUs), reduce inside the kernel, behind the
+    same parity check as the main run. Returns microseconds per layer (max over ranks) and the check's verdict."""
+    spec = synth.QWEN if model == "qwen" else synth.DEEPSEEK
+    variant = f"{'qwen' if model == 'qwen' else 'ds'}_tp{world}"
+    n = spec.inter // world
+    kw = {"inter_slice": (rank * n, (rank + 1) * n), "chunk": 8}
+    mk = MonoKernel(variant_path(variant))
+    layer = synth.make_layer(spec, seed=0, device=dev, with_shared=False, **kw)
+    batch = synth.make_batch(spec, layer, T, seed=0, device=dev)
+    sc = mk.scratch(T, dev)
+    plan = tp_fused.FusedTPPlan(mk, dist.group.WORLD, hidden=spec.hidden, max_tokens=T, nslots=2)
+    if not plan.usable:
+        return {"variant": variant, "unavailable": plan.reason}
+    if plan.chunks_for(T) == 0:
+        plan.chunks_by_tokens[T] = 8 if T >= 16384 else 4
+
+    def go():
+        plan.fused_tp_launch(batch["hs"], batch["logits"], layer["w13"], layer["w13_scale"], layer["w2"],
+                             layer["w2_scale"], spec.top_k, True, layer["bias"])
+    for _ in range(3):
+        go()
+    barrier()
+    mk.check_status(sc["workspace"])
+    parity = verify_reduced_output(spec, mk, layer, batch, None, sc, plan, plan.pool.output(T), world, rank, dist, dev,
+                                   f"tp{world}", kw, fused=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(steps):
+        go()
+    e1.record()
+    barrier()
+    mk.check_status(sc["workspace"])
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    return {"variant": variant, "tokens": T, "us_per_layer": ms * 1e3,
+            "tflops": synth.routed_flops(spec, T) / (ms * 1e-3) / 1e12, "reduce": "in-kernel NVLS multimem all-reduce",
+            "parity_checked": bool(parity["ok"]), "parity": parity}
+
+
 def time_with_shared_expert(spec, mk, layer, batch, out, sc, steps, dev, routed_flops) -> dict:
     """Beside the contract's figure (routed experts only): the same launch with the layer's sigmoid-gated
     shared expert computed inside it (I_sh = 512: +12.5 % FLOPs)."""
@@ -769,7 +819,7 @@ def verify_reduced_output(spec, mk, layer, batch, emap, sc, pool_plan, result, w
 
 
 def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
-           reduce_desc, phases=None, sustained=None, parity=None, with_shared=None) -> None:
+           reduce_desc, phases=None, sustained=None, parity=None, with_shared=None, extra=None) -> None:
     peaks = measured_peaks()
     fp8_lib = fp8_gemm_tflops(dev) if (world == 1 and not args.kernel_only) else None
     if peaks.get("bf16_tflops"):
@@ -821,6 +871,8 @@ def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flop
         line["sustained"] = sustained
     if with_shared is not None:
         line["with_shared_expert"] = with_shared
+    if extra is not None:
+        line["extra"] = extra
     if world > 1:
         line["parity_checked"] = bool(parity is not None and parity["ok"])
         line["parity"] = parity

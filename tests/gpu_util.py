@@ -72,40 +72,33 @@ def bf16_spacing(x: torch.Tensor) -> torch.Tensor:
     return torch.exp2(torch.floor(torch.log2(mag)) - 7.0)
 
 
-def assert_close(O, got, ref, steps: float = 1.0):
-    """The acceptance rule of `check_output` for two fp32 tensors; `steps` bf16 steps are allowed where one
-    step exceeds 2e-2 rms (sums of several bf16 outputs can differ by one step per summand)."""
+def assert_close(O, got, ref, steps: float = 2.0, rare: float = 1e-4):
+    """The acceptance rule of `check_output` for two fp32 tensors; `steps` bf16 steps are allowed where the
+    spacing exceeds 2e-2 rms (sums of several bf16 outputs can differ by one step per summand), and at most the
+    fraction `rare` of the elements may be of that kind (None: any number, for comparisons between two different
+    rounding schemes)."""
     m = O.parity_metrics(got, ref)
     err = (got - ref).abs()
     beyond = err > MAX_ABS_OVER_RMS * m["rms_ref"]
     m["beyond_2e-2_rms"] = int(beyond.sum())
     if beyond.any():
         assert bool((err[beyond] <= bf16_spacing(ref[beyond]) * steps * 1.0001).all()), m
-        assert m["beyond_2e-2_rms"] <= max(1, ref.numel() // 10000), m
+        if rare is not None:
+            assert m["beyond_2e-2_rms"] <= max(1, int(ref.numel() * rare)), m
     assert m["cos"] >= MIN_COS, m
     return m
 
 
 def check_output(O, out, toks, q, s, ids, w, layer, **kw):
     """bf16 output against the path-faithful oracle: cosine >= 0.9995 and every element within
-    max(2e-2 * rms(ref), one bf16 step of the reference value).
+    max(2e-2 * rms(ref), two bf16 steps of the reference value).
 
-    The second term matters only when many elements are compared. The output is bf16: at |value| above 3 rms its
-    neighbouring values are more than 2e-2 * rms apart, so there the smallest difference two correct
-    implementations can show (the kernel's tensor-core summation order against the oracle's, meeting a rounding
-    boundary) already exceeds the first term. Such elements must be exactly one step away, and they must be
-    rare (below one in 10 000)."""
+    The second term matters only when many elements are compared. The partial rows and the output are bf16: at
+    |value| above 3 rms neighbouring bf16 values are more than 2e-2 * rms apart, so there the smallest
+    difference two correct implementations can show (the kernel's tensor-core summation order against the
+    oracle's, meeting a rounding boundary in a partial row, in the final rounding, or in both) already exceeds
+    the first term. Such elements must be within two steps, and they must be rare (below one in 10 000)."""
     ref = O.moe_path(toks, q, s, ids, w, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], **kw).float()
     got = out.float().cpu()[torch.from_numpy(toks).long()]
     assert torch.isfinite(got).all()
-    m = O.parity_metrics(got, ref)
-    err = (got - ref).abs()
-    bound = MAX_ABS_OVER_RMS * m["rms_ref"]
-    beyond = err > bound
-    m["beyond_2e-2_rms"] = int(beyond.sum())
-    if beyond.any():
-        one_step = err[beyond] <= bf16_spacing(ref[beyond]) * 1.0001
-        assert bool(one_step.all()), (m, float((err[beyond] / bf16_spacing(ref[beyond])).max()))
-        assert m["beyond_2e-2_rms"] <= max(1, ref.numel() // 10000), m
-    assert m["cos"] >= MIN_COS, m
-    return m
+    return assert_close(O, got, ref, steps=2.0)

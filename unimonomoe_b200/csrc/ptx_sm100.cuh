@@ -241,13 +241,6 @@ __device__ __forceinline__ uint32_t cvt_bf16x2_satfinite(float lo, float hi) {
   return r;
 }
 
-// tanh on the special-function unit: one MUFU operation, relative error about 2^-11.
-__device__ __forceinline__ float tanh_approx(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 // 32-byte (256-bit) global store; the address must be 32-byte aligned.
 __device__ __forceinline__ void st_global_256(void* p, const uint32_t (&w)[8]) {
   asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
