@@ -439,8 +439,8 @@ def main() -> None:
 
 
 PROF_NAMES = ["tma_wait_emptyB", "mma_wait_fullB", "mma_wait_fullA", "mma_wait_tmem", "mma_wait_inter", "mma_total",
-              "gather_wait_emptyA", "-", "epi_wait_full", "epi_up", "epi_silu", "epi_down", "epi_store", "epi_total",
-              "epi_bar", "epi_zero"]
+              "gather_wait_emptyA", "phase0_route", "epi_wait_full", "epi_up", "epi_silu", "epi_down", "epi_store",
+              "epi_total", "epi_bar", "phase0_quant"]
 
 
 def stall_counters(mk, workspace) -> None:
@@ -778,9 +778,14 @@ def verify_reduced_output(spec, mk, layer, batch, emap, sc, pool_plan, result, w
     d = (_bf16_order_key(got) - _bf16_order_key(plain)).abs()
     rms = float(plain.float().pow(2).mean().sqrt())
     max_abs = float((got.float() - plain.float()).abs().max())
+    # NCCL may sum in another order and round between hops: within 2e-2 rms, or, where bf16 values are further
+    # apart than that, within one bf16 step per rank
+    pf = plain.float()
+    step = torch.exp2(torch.floor(torch.log2(pf.abs().clamp(min=2.0 ** -126))) - 7.0)
+    close = bool(((got.float() - pf).abs() <= torch.maximum(step * (world * 1.0001), torch.full_like(pf, 2e-2 * rms))).all())
     info["vs_kernel_plus_nccl"] = {"moved": int((d > 0).sum()), "over_1_ulp": int((d > 1).sum()), "max_ulp": int(d.max()),
-                                   "max_abs_over_rms": max_abs / max(rms, 1e-30)}
-    ok = ok and max_abs <= 2e-2 * rms
+                                   "max_abs_over_rms": max_abs / max(rms, 1e-30), "within_bound": close}
+    ok = ok and close
     if rank == 0:
         import numpy as np
         from oracle import cpu_oracle as O

@@ -703,6 +703,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
 
   constexpr int NT = 1;  // tokens routed side by side by one warp (two were measured: 8 % slower, the second token's state costs more than the filled latency gains)
   float lg_next[NT][8];
+  PROF_DECL(p0_route); PROF_DECL(p0_quant);
   if (t_begin < t_end) {
 #pragma unroll
     for (int a = 0; a < NT; ++a) {
@@ -732,7 +733,10 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
 #pragma unroll
     for (int a = 0; a < NT; ++a)
       if (t + a < t_end) quant_token_load(p, t + a, 0, lane, qraw[a]);
+    { PROF_T0();
     route_tokens<NT>(lg, p.router_bias, lane, my_id, my_w);
+    PROF_ADD(p0_route); }
+    PROF_T0();
 #pragma unroll
     for (int a = 0; a < NT; ++a) {
       if (t + a >= t_end) break;
@@ -765,7 +769,9 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       }
     }
     __syncwarp();
+    PROF_ADD(p0_quant);
   }
+  if (tid == 0) { PROF_STORE(7, p0_route); PROF_STORE(15, p0_quant); }
   __syncthreads();
   if (tid < E) {
     int c = 0;
@@ -1480,7 +1486,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       }
       if (et == 0) {
         PROF_STORE(8, pe_wait); PROF_STORE(9, pe_up); PROF_STORE(10, pe_silu); PROF_STORE(11, pe_down);
-        PROF_STORE(12, pe_store); PROF_STORE(14, pe_bar); PROF_STORE(15, pe_zero);
+        PROF_STORE(12, pe_store); PROF_STORE(14, pe_bar);
 #ifdef MONO_PROFILE
         p.ws->prof[blockIdx.x][13] = static_cast<uint64_t>(clock64() - pe_start);
 #endif
