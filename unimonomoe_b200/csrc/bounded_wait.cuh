@@ -37,7 +37,9 @@ struct Workspace {
   uint32_t abort_flag;                      // raised together with status
   uint32_t status_aux[2];                   // free-form detail for the first error
   uint32_t tp_ready[kTpMaxChunks];          // compute blocks that finished chunk c
-  uint32_t tp_done_local;                   // communication blocks past their last shard
+  uint32_t tp_open[kTpMaxChunks];           // 1 once every rank has finished chunk c (set behind the rank barrier)
+  uint32_t tp_piece[kTpMaxChunks];          // next piece of this rank's share of chunk c to reduce
+  uint32_t tp_pieces_done;                  // pieces reduced and made visible
   uint32_t tp_done_flag;                    // set once the final rank barrier is past
   uint32_t tp_seq_pub;                      // this launch's sequence number
   uint32_t reserved2;

@@ -1526,6 +1526,87 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
     const int nchunk = tp_on ? p.tp_nchunk : 1;
     const uint32_t seq = (p.tp_seqctr != nullptr) ? ld_relaxed_gpu(&ws->tp_seq_pub) : p.tp_seq;
 
+    // ---- the all-reduce of the ranks' partial outputs, inside the kernel (only when tp_on)
+    // Chunked one-shot all-reduce (kernel/qwen_tp/src/prefill_mono_final_nb.cu:1461-1504): once every rank has
+    // summed chunk c, each rank reduces its 1/world share of the chunk across the ranks with multimem.ld_reduce
+    // and writes the result back to every rank with multimem.st. A rank's share of a chunk is cut into pieces of
+    // PIECE 16-byte vectors that CTAs take from a counter: the `ncomm` communication CTAs from the start, and
+    // every summing CTA as soon as it has finished its own sums, so that the tail of the transfer has the whole
+    // grid's loads in flight.
+    constexpr int UN = 8;                                      // 16-byte reduce-loads in flight per thread
+    constexpr size_t PIECE = static_cast<size_t>(UN) * BLOCK;  // vectors per piece (48 KB)
+    constexpr size_t ALIGN = 32;                               // shares start on 512-byte boundaries
+    const size_t out_mv = static_cast<size_t>(T) * H_DIM / 8;
+    auto share_of = [&](int c, size_t& s_lo, size_t& s_hi) {
+      const size_t lo = out_mv * c / nchunk, hi = out_mv * (c + 1) / nchunk;
+      const size_t ng = (hi - lo + ALIGN - 1) / ALIGN;
+      s_lo = lo + (ng * p.tp_rank / p.tp_world) * ALIGN;
+      s_hi = lo + (ng * (p.tp_rank + 1) / p.tp_world) * ALIGN;
+      s_lo = s_lo < hi ? s_lo : hi;
+      s_hi = s_hi < hi ? s_hi : hi;
+    };
+    auto rank_barrier = [&](int slot) -> bool {
+      // arrive on every peer's window, then wait for every peer on mine
+      for (int rk = 0; rk < p.tp_world; ++rk)
+        st_release_sys(p.tp_pads[rk] + static_cast<size_t>(slot) * p.tp_world + p.tp_rank, seq);
+      for (int rk = 0; rk < p.tp_world; ++rk) {
+        const uint32_t* w = p.tp_pads[p.tp_rank] + static_cast<size_t>(slot) * p.tp_world + rk;
+        const uint64_t t0 = globaltimer_ns();
+        uint32_t polls = 0;
+        while (ld_acquire_sys(w) < seq) {
+          if ((++polls & 15u) == 0u) {
+            if (aborted(ws)) return false;
+            if (globaltimer_ns() - t0 > p.timeout_ns) {
+              report_error(ws, kErrRankBarrier, static_cast<uint32_t>(slot), static_cast<uint32_t>(rk), seq);
+              return false;
+            }
+          }
+        }
+      }
+      return true;
+    };
+    // Whole CTA: take pieces of this rank's share of chunk c until none is left. False when the launch aborts.
+    auto reduce_pieces = [&](int c) -> bool {
+      if (tid == 0)
+        S.flag = wait_counter_ge(&ws->tp_open[c], 1u, wc, kErrChunkReady, static_cast<uint32_t>(16 + c)) ? 1u : 0u;
+      __syncthreads();
+      const bool open = S.flag != 0u;
+      __syncthreads();
+      if (!open) return false;
+      size_t s_lo, s_hi;
+      share_of(c, s_lo, s_hi);
+      const uint32_t npieces = static_cast<uint32_t>((s_hi - s_lo + PIECE - 1) / PIECE);
+      uint32_t mine = 0;
+      for (;;) {
+        if (tid == 0) S.flag = atomicAdd(&ws->tp_piece[c], 1u);
+        __syncthreads();
+        const uint32_t j = S.flag;
+        __syncthreads();
+        if (j >= npieces) break;
+        const size_t base = s_lo + static_cast<size_t>(j) * PIECE + tid;
+        uint32_t x[UN][4];
+        bool live[UN];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const size_t v = base + static_cast<size_t>(u) * BLOCK;
+          live[u] = v < s_hi;
+          if (live[u]) multimem_ld_reduce_bf16x8(p.tp_mc + v * 8, x[u][0], x[u][1], x[u][2], x[u][3]);
+        }
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const size_t v = base + static_cast<size_t>(u) * BLOCK;
+          if (live[u]) multimem_st_b128(p.tp_mc + v * 8, x[u][0], x[u][1], x[u][2], x[u][3]);
+        }
+        ++mine;
+      }
+      if (mine > 0) {
+        __threadfence_system();   // the stores of these pieces have reached every rank
+        __syncthreads();
+        if (tid == 0) atomicAdd(&ws->tp_pieces_done, mine);
+      }
+      return true;
+    };
+
     if (!tp_on || bid < ncomp) {
       const size_t stride = static_cast<size_t>(ncomp) * BLOCK;
       for (int c = 0; c < nchunk; ++c) {
@@ -1599,84 +1680,46 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         __syncthreads();
         if (tid == 0) atomicAdd(&ws->tp_ready[c], 1u);
       }
+      if (tp_on) {   // sums done: join the transfer of whatever is not reduced yet
+        for (int c = 0; c < nchunk; ++c)
+          if (!reduce_pieces(c)) break;
+      }
     } else {
       // ---------------------------------------------------------- communication blocks
-      // Chunked one-shot all-reduce (kernel/qwen_tp/src/prefill_mono_final_nb.cu:1461-1504):
-      // chunk c is split over world*ncomm shards aligned to 512 B; each shard is summed
-      // across ranks by multimem.ld_reduce and written back to every rank by multimem.st.
-      // The communication CTAs work in two groups that take alternate chunks, so that the fixed cost of a
-      // chunk (ready wait, rank barrier over NVLink, filling and draining the load pipeline: ~15 us) of one
-      // group overlaps the transfer of the other.
+      // Block cb opens the chunks c = cb, cb + ncomm, ...: it waits until this rank's summing blocks have
+      // finished the chunk, meets the peers' block cb at a rank barrier (window slot c) and raises tp_open[c].
+      // With ncomm >= nchunk (the usual shapes) every chunk has its own opener, so a chunk opens as soon as the
+      // slowest rank has summed it. Then it takes pieces like everybody else.
       const int cb = bid - ncomp;
-      const int ngroups = (p.tp_ncomm % 2 == 0 && nchunk >= 2) ? 2 : 1;
-      const int grp = cb % ngroups, ci = cb / ngroups, per_group = p.tp_ncomm / ngroups;
-      const int nsh = p.tp_world * per_group;
-      const int sh = p.tp_rank * per_group + ci;
-      const size_t out_mv = static_cast<size_t>(T) * H_DIM / 8;
-      constexpr size_t ALIGN = 32;
       bool ok = true;
-      auto rank_barrier = [&](int slot) -> bool {
-        // arrive on every peer's window, then wait for every peer on mine
-        for (int rk = 0; rk < p.tp_world; ++rk)
-          st_release_sys(p.tp_pads[rk] + static_cast<size_t>(slot) * p.tp_world + p.tp_rank, seq);
-        for (int rk = 0; rk < p.tp_world; ++rk) {
-          const uint32_t* w = p.tp_pads[p.tp_rank] + static_cast<size_t>(slot) * p.tp_world + rk;
-          const uint64_t t0 = globaltimer_ns();
-          uint32_t polls = 0;
-          while (ld_acquire_sys(w) < seq) {
-            if ((++polls & 15u) == 0u) {
-              if (aborted(ws)) return false;
-              if (globaltimer_ns() - t0 > p.timeout_ns) {
-                report_error(ws, kErrRankBarrier, static_cast<uint32_t>(slot), static_cast<uint32_t>(rk), seq);
-                return false;
-              }
-            }
-          }
-        }
-        return true;
-      };
-      for (int c = grp; c < nchunk; c += ngroups) {
+      for (int c = cb; c < nchunk && ok; c += p.tp_ncomm) {
         if (tid == 0) {
           ok = wait_counter_ge(&ws->tp_ready[c], static_cast<uint32_t>(ncomp), wc, kErrChunkReady, static_cast<uint32_t>(c));
-          if (ok) ok = rank_barrier(c * p.tp_ncomm + cb);
+          if (ok) ok = rank_barrier(c);
+          if (ok) {
+            __threadfence();
+            atomicExch(&ws->tp_open[c], 1u);
+          }
           S.flag = ok ? 1u : 0u;
         }
         __syncthreads();
         ok = S.flag != 0u;
         __syncthreads();
-        if (!ok) break;
-        const size_t lo = out_mv * c / nchunk, hi = out_mv * (c + 1) / nchunk;
-        const size_t ng = (hi - lo + ALIGN - 1) / ALIGN;
-        size_t s_lo = lo + (ng * sh / nsh) * ALIGN, s_hi = lo + (ng * (sh + 1) / nsh) * ALIGN;
-        s_lo = s_lo < hi ? s_lo : hi;
-        s_hi = s_hi < hi ? s_hi : hi;
-        constexpr int UN = 8;  // 16-byte reduce-loads in flight per thread (16 measured: no difference)
-        for (size_t base = s_lo + tid; base < s_hi; base += static_cast<size_t>(UN) * BLOCK) {
-          uint32_t x[UN][4];
-          bool live[UN];
-#pragma unroll
-          for (int u = 0; u < UN; ++u) {
-            const size_t v = base + static_cast<size_t>(u) * BLOCK;
-            live[u] = v < s_hi;
-            if (live[u]) multimem_ld_reduce_bf16x8(p.tp_mc + v * 8, x[u][0], x[u][1], x[u][2], x[u][3]);
-          }
-#pragma unroll
-          for (int u = 0; u < UN; ++u) {
-            const size_t v = base + static_cast<size_t>(u) * BLOCK;
-            if (live[u]) multimem_st_b128(p.tp_mc + v * 8, x[u][0], x[u][1], x[u][2], x[u][3]);
-          }
-        }
       }
-      __threadfence_system();
-      __syncthreads();
-      if (tid == 0 && ok) {
-        if (atomicAdd(&ws->tp_done_local, 1u) == static_cast<uint32_t>(p.tp_ncomm) - 1u) {
-          if (rank_barrier(nchunk * p.tp_ncomm)) {
-            __threadfence();
-            atomicExch(&ws->tp_done_flag, 1u);
-          }
-        } else {
-          wait_counter_ge(&ws->tp_done_flag, 1u, wc, kErrDoneFlag, 0);
+      for (int c = 0; c < nchunk && ok; ++c) ok = reduce_pieces(c);
+      // Block 0 closes the launch: when every piece of this rank's shares is out, it meets the peers at the last
+      // rank barrier. Behind it every rank's stores into this rank's buffer have landed; the kernel cannot
+      // complete before this block returns.
+      if (cb == 0 && tid == 0 && ok) {
+        uint32_t total = 0;
+        for (int c = 0; c < nchunk; ++c) {
+          size_t s_lo, s_hi;
+          share_of(c, s_lo, s_hi);
+          total += static_cast<uint32_t>((s_hi - s_lo + PIECE - 1) / PIECE);
+        }
+        if (wait_counter_ge(&ws->tp_pieces_done, total, wc, kErrDoneFlag, 0) && rank_barrier(nchunk * p.tp_ncomm)) {
+          __threadfence();
+          atomicExch(&ws->tp_done_flag, 1u);
         }
       }
       __syncthreads();
