@@ -154,6 +154,23 @@ int prefill_wgmma_shm_total(void);            /* Q:1789 */
 
 /* ---- additions of this library: no counterpart in the reference ---------------------- */
 
+/* launch_prefill_moe_wgmma_q1_ep2 plus tp_peers: a device array of tp_world pointers, every rank's address of the
+ * output window (the reference's symmetric pool exposes the same table, fused_moe/symm_output_pool.py:95-149; its
+ * kernel does not use it). With two ranks the in-kernel reduce then reads the peer's copy directly over NVLink,
+ * adds its own copy from local memory and writes the sum to both ranks: the same bits as the multicast reduce for a
+ * third of the link traffic (through the multicast alias the switch fetches this rank's own copy over NVLink too).
+ * With more ranks, or a null table, it behaves exactly like the _ep2 entry. */
+int prefill_wgmma_tp_has_peer_reduce(void);   /* 1 = launch_prefill_moe_wgmma_q1_ep3 is usable */
+int launch_prefill_moe_wgmma_q1_ep3(const float* logits, int num_tokens, int block_m, void* workspace,
+                                    size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
+                                    float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
+                                    const uint8_t* down_w_fp8, const float* down_w_scales, float* output_accum,
+                                    int32_t* topk_ids, float* topk_weights, int32_t* sorted_token_ids,
+                                    void* bf16_output, const float* router_bias, void* tp_mc, void* tp_pads,
+                                    int tp_rank, int tp_world, int tp_nchunk, int tp_ncomm, uint32_t tp_seq,
+                                    void* tp_seqctr, const void* tp_residual, float out_scale,
+                                    const int32_t* expert_map, void* tp_peers, prefill_mono_stream_t stream);
+
 /* The router linear inside the launch. The reference leaves it to the model (a separate GEMM before the
  * hook, vllm_integration/vllm/_custom_ops.py:4618 takes finished logits). router_w_bf16 is the gate weight
  * [E, K] in bf16; logits_out [T, E] fp32 receives the logits the kernel computed and routed on. The

@@ -17,9 +17,11 @@
 //                             per (row,128) into shared memory, which the MMA thread
 //                             then uses as the A operand of the down projection; the
 //                             down result times the routing weight goes out as bf16
-//   phase 3   per token sum of its top-k partial rows -> bf16 [T,H]; under tensor
-//             parallelism the last `ncomm` CTAs instead run a chunked one-shot
-//             all-reduce through the NVLS multicast alias while the others compute.
+//   phase 3   per token sum of its top-k partial rows -> bf16 [T,H]; under tensor or expert
+//             parallelism a chunked one-shot all-reduce of the ranks' outputs runs in the same
+//             launch: the last `ncomm` CTAs open finished chunks (rank barrier) and reduce them
+//             through the NVLS multicast alias (two ranks: by direct peer loads) while the others
+//             still sum, and every summing CTA joins the transfer when its sums are done.
 //
 // An intermediate wider than 512 columns is processed in chunks of 512 (one partial row per chunk);
 // -DMONO_PAIR=1 schedules pairs of tiles on clusters of two CTAs (tcgen05 cta_group::2).
@@ -235,6 +237,7 @@ struct Params {
   int tp_rank, tp_world, tp_nchunk, tp_ncomm;
   uint32_t tp_seq;
   uint32_t* tp_seqctr;
+  __nv_bfloat16** tp_peers;   // every rank's address of the output window (device array), or null
   const __nv_bfloat16* residual;
   float out_scale;
   uint64_t timeout_ns;
@@ -1565,6 +1568,8 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       }
       return true;
     };
+    // the peer's window when the group has two ranks and the caller passed the table of windows
+    __nv_bfloat16* const peer_pair = (tp_on && p.tp_peers != nullptr && p.tp_world == 2) ? p.tp_peers[1 - p.tp_rank] : nullptr;
     // Whole CTA: take pieces of this rank's share of chunk c until none is left. False when the launch aborts.
     auto reduce_pieces = [&](int c) -> bool {
       if (tid == 0)
@@ -1586,6 +1591,35 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         const size_t base = s_lo + static_cast<size_t>(j) * PIECE + tid;
         uint32_t x[UN][4];
         bool live[UN];
+        if (peer_pair != nullptr) {
+          // Two ranks: read the peer's copy over NVLink, add this rank's own copy from local memory, write the
+          // sum to both. The multicast form makes the switch fetch BOTH copies over NVLink (this rank's too) and
+          // deliver the result twice: three times the link traffic of this form for the same bits.
+          uint32_t y[UN][4];
+#pragma unroll
+          for (int u = 0; u < UN; ++u) {
+            const size_t v = base + static_cast<size_t>(u) * BLOCK;
+            live[u] = v < s_hi;
+            if (live[u]) {
+              ld_relaxed_sys_b128(peer_pair + v * 8, x[u][0], x[u][1], x[u][2], x[u][3]);
+              const uint4 own = __ldcg(reinterpret_cast<const uint4*>(p.out + v * 8));
+              y[u][0] = own.x; y[u][1] = own.y; y[u][2] = own.z; y[u][3] = own.w;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < UN; ++u) {
+            const size_t v = base + static_cast<size_t>(u) * BLOCK;
+            if (live[u]) {
+              uint4 r;
+              r.x = add_bf16x2_f32(x[u][0], y[u][0]); r.y = add_bf16x2_f32(x[u][1], y[u][1]);
+              r.z = add_bf16x2_f32(x[u][2], y[u][2]); r.w = add_bf16x2_f32(x[u][3], y[u][3]);
+              *reinterpret_cast<uint4*>(p.out + v * 8) = r;
+              st_relaxed_sys_b128(peer_pair + v * 8, r.x, r.y, r.z, r.w);
+            }
+          }
+          ++mine;
+          continue;
+        }
 #pragma unroll
         for (int u = 0; u < UN; ++u) {
           const size_t v = base + static_cast<size_t>(u) * BLOCK;
@@ -1945,7 +1979,7 @@ static int launch_common(const void* router_w, float* logits_buf, const float* l
                                     int tp_rank, int tp_world, int tp_nchunk, int tp_ncomm, uint32_t tp_seq,
                                     void* tp_seqctr, const void* tp_residual, float out_scale,
                                     const int32_t* expert_map, cudaStream_t stream,
-                                    const SharedExpertArgs* sh = nullptr) {
+                                    const SharedExpertArgs* sh = nullptr, void* tp_peers = nullptr) {
   (void)block_m;  // the tile height is the compiled TILE_M
   if (router_w != nullptr && PAIR) return -106;  // the pair build has no router linear
   if (sh != nullptr && PAIR) return -108;        // nor the shared expert
@@ -2009,6 +2043,7 @@ static int launch_common(const void* router_w, float* logits_buf, const float* l
   p.tp_ncomm = tp_ncomm;
   p.tp_seq = tp_seq;
   p.tp_seqctr = static_cast<uint32_t*>(tp_seqctr);
+  p.tp_peers = static_cast<__nv_bfloat16**>(tp_peers);
   p.residual = static_cast<const __nv_bfloat16*>(tp_residual);
   p.out_scale = out_scale;
   p.timeout_ns = g_timeout_ns;
@@ -2112,6 +2147,27 @@ int launch_prefill_moe_wgmma_q1_ep2(const float* logits, int num_tokens, int blo
                        act_scales, up_w_fp8, up_w_scales, down_w_fp8, down_w_scales, output_accum, topk_ids,
                        topk_weights, sorted_token_ids, bf16_output, router_bias, tp_mc, tp_pads, tp_rank, tp_world,
                        tp_nchunk, tp_ncomm, tp_seq, tp_seqctr, tp_residual, out_scale, expert_map, stream);
+}
+
+// The _ep2 entry plus tp_peers: a device array of tp_world pointers, every rank's address of the output window
+// (bf16_output on that rank). With two ranks the in-kernel reduce then reads the peer's copy directly instead
+// of going through the multicast alias (a third of the NVLink traffic, the same bits); with more ranks, or a null
+// table, it is the multicast reduce of the _ep2 entry.
+int prefill_wgmma_tp_has_peer_reduce() { return 1; }
+int launch_prefill_moe_wgmma_q1_ep3(const float* logits, int num_tokens, int block_m, void* workspace,
+                                    size_t workspace_bytes, const void* act_bf16, uint8_t* act_fp8,
+                                    float* act_scales, const uint8_t* up_w_fp8, const float* up_w_scales,
+                                    const uint8_t* down_w_fp8, const float* down_w_scales, float* output_accum,
+                                    int32_t* topk_ids, float* topk_weights, int32_t* sorted_token_ids,
+                                    void* bf16_output, const float* router_bias, void* tp_mc, void* tp_pads,
+                                    int tp_rank, int tp_world, int tp_nchunk, int tp_ncomm, uint32_t tp_seq,
+                                    void* tp_seqctr, const void* tp_residual, float out_scale,
+                                    const int32_t* expert_map, void* tp_peers, cudaStream_t stream) {
+  return launch_common(nullptr, nullptr, logits, num_tokens, block_m, workspace, workspace_bytes, act_bf16, act_fp8,
+                       act_scales, up_w_fp8, up_w_scales, down_w_fp8, down_w_scales, output_accum, topk_ids,
+                       topk_weights, sorted_token_ids, bf16_output, router_bias, tp_mc, tp_pads, tp_rank, tp_world,
+                       tp_nchunk, tp_ncomm, tp_seq, tp_seqctr, tp_residual, out_scale, expert_map, stream, nullptr,
+                       tp_peers);
 }
 
 // The router linear inside the launch: router_w_bf16 is the gate weight [E, K] in bf16 (the checkpoints

@@ -272,6 +272,22 @@ __device__ __forceinline__ void multimem_st_b128(void* mc, uint32_t a, uint32_t 
                : "memory");
 }
 
+// 16-byte load / store at system scope: a peer GPU's memory over NVLink (no multicast involved).
+__device__ __forceinline__ void ld_relaxed_sys_b128(const void* p, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+  asm volatile("ld.relaxed.sys.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "l"(p) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys_b128(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.relaxed.sys.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// Sum of two packed bf16 pairs, each lane added in fp32 and rounded once to bf16 (what the switch does for two ranks).
+__device__ __forceinline__ uint32_t add_bf16x2_f32(uint32_t x, uint32_t y) {
+  const float xl = __uint_as_float(x << 16), xh = __uint_as_float(x & 0xFFFF0000u);
+  const float yl = __uint_as_float(y << 16), yh = __uint_as_float(y & 0xFFFF0000u);
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__fadd_rn(xh, yh)), "f"(__fadd_rn(xl, yl)));
+  return r;
+}
+
 // ---------------------------------------------------------------- register budget
 template <int N>
 __device__ __forceinline__ void reg_inc() {

@@ -393,7 +393,7 @@ class MonoKernel:
         ]
         bias_arg = vp(bias.data_ptr() if bias is not None else 0)
         if shared is not None:
-            mc, pads, seqctr, rank, world, nchunk, ncomm = tp if tp is not None else (0, 0, 0, 0, 1, 1, 0)
+            mc, pads, seqctr, rank, world, nchunk, ncomm = tp[:7] if tp is not None else (0, 0, 0, 0, 1, 1, 0)
             entry = self.lib.launch_prefill_moe_wgmma_q1_shared
             g = shared.get("gate")
             args += [bias_arg, vp(int(mc)), vp(int(pads)), ctypes.c_int(int(rank)), ctypes.c_int(int(world)),
@@ -404,16 +404,22 @@ class MonoKernel:
                      vp(sc["shared_gate"].data_ptr()), ctypes.c_int(int(shared_part[0])), ctypes.c_int(int(shared_part[1]))]
         elif rw is not None:
             # one entry point carries every option: absent ones are passed as null / neutral values
-            mc, pads, seqctr, rank, world, nchunk, ncomm = tp if tp is not None else (0, 0, 0, 0, 1, 1, 0)
+            mc, pads, seqctr, rank, world, nchunk, ncomm = tp[:7] if tp is not None else (0, 0, 0, 0, 1, 1, 0)
             entry = self.lib.launch_prefill_moe_wgmma_q1_gemv
             args += [bias_arg, vp(int(mc)), vp(int(pads)), ctypes.c_int(int(rank)), ctypes.c_int(int(world)),
                      ctypes.c_int(int(nchunk)), ctypes.c_int(int(ncomm)), ctypes.c_uint(0), vp(int(seqctr)),
                      vp(int(resid_ptr)), ctypes.c_float(float(out_scale)), vp(emap.data_ptr() if emap is not None else 0)]
         elif tp is not None:
-            mc, pads, seqctr, rank, world, nchunk, ncomm = tp
+            mc, pads, seqctr, rank, world, nchunk, ncomm = tp[:7]
+            peers = int(tp[7]) if len(tp) > 7 else 0
             args += [bias_arg, vp(int(mc)), vp(int(pads)), ctypes.c_int(int(rank)), ctypes.c_int(int(world)),
                      ctypes.c_int(int(nchunk)), ctypes.c_int(int(ncomm)), ctypes.c_uint(0), vp(int(seqctr))]
-            if emap is not None:
+            if peers and self._bind("launch_prefill_moe_wgmma_q1_ep3"):
+                # the table of every rank's output window: two ranks then reduce by direct peer loads
+                entry = self.lib.launch_prefill_moe_wgmma_q1_ep3
+                args += [vp(int(resid_ptr)), ctypes.c_float(float(out_scale)), vp(emap.data_ptr() if emap is not None else 0),
+                         vp(peers)]
+            elif emap is not None:
                 entry = self.lib.launch_prefill_moe_wgmma_q1_ep2
                 entry.restype = ctypes.c_int
                 args += [vp(int(resid_ptr)), ctypes.c_float(float(out_scale)), vp(emap.data_ptr())]
@@ -458,14 +464,14 @@ class MonoKernel:
                     expert_scales_down, out, top_k=8, renormalize=True, e_score_correction_bias=None, tp_mc_ptr=0,
                     tp_pads_ptr=0, tp_seqctr_ptr=0, tp_rank=0, tp_world=1, tp_nchunk=0, tp_ncomm=0, tp_residual=None,
                     tp_out_scale=1.0, check=False, expert_map=None, router_weight=None, shared=None,
-                    shared_part=(0, 1)) -> None:
+                    shared_part=(0, 1), tp_peers_ptr=0) -> None:
         """Write into a caller-supplied destination (_custom_ops.py:4861-4924). tp_ncomm > 0 selects the
         fused collective, in which case ``out`` must be the symmetric window tp_mc_ptr aliases."""
         tp = None
         if tp_ncomm > 0:
             if not (tp_mc_ptr and tp_pads_ptr):
                 raise RuntimeError("fused TP launch requires both a multicast pointer and a barrier pad pointer")
-            tp = (tp_mc_ptr, tp_pads_ptr, tp_seqctr_ptr, tp_rank, tp_world, tp_nchunk, tp_ncomm)
+            tp = (tp_mc_ptr, tp_pads_ptr, tp_seqctr_ptr, tp_rank, tp_world, tp_nchunk, tp_ncomm, tp_peers_ptr)
         self.prefill_impl(activations_in, router_logits, expert_weights_up, expert_scales_up, expert_weights_down,
                           expert_scales_down, top_k, renormalize, e_score_correction_bias, out, tp, tp_residual,
                           tp_out_scale, expert_map, check=check, router_weight=router_weight, shared=shared,

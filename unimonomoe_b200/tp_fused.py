@@ -44,6 +44,9 @@ ENV_FOLD = "VLLM_PREFILL_MONOKERNEL_TP_FOLD_SHARED"
 FUSED_CHUNKS_BY_TOKENS = {8192: 4, 16384: 8}
 # Communication CTAs. The reference settled on 14 of its 132 (monokernel_tp.py:87).
 FUSED_NCOMM = 14
+# Group size at which the kernel reduces by direct peer loads instead of the multicast alias: with two ranks the
+# switch would fetch this rank's own copy over NVLink as well, three times the traffic for the same bits.
+PEER_REDUCE_WORLD = 2
 
 
 def _positive_int(text: str, what: str) -> int:
@@ -185,6 +188,10 @@ class SymmOutputPool:
     def base_ptr(self, slot: int = 0) -> int:
         return self._outputs[slot].local
 
+    def peers_ptr(self, slot: int = 0) -> int:
+        """Device address of the array of every rank's address of this slot (for the two-rank peer-load reduce)."""
+        return self._outputs[slot].peer_table
+
     def slot_buffer(self, slot: int = 0) -> torch.Tensor:
         return self._outputs[slot].tensor
 
@@ -203,7 +210,8 @@ class SymmOutputPool:
 
     # ---- integrity
     def _addresses(self) -> tuple:
-        return (tuple((w.local, w.multicast) for w in self._outputs), self._signals.peer_table, self.seqctr_ptr)
+        return (tuple((w.local, w.multicast, w.peer_table) for w in self._outputs), self._signals.peer_table,
+                self.seqctr_ptr)
 
     def assert_stable(self) -> None:
         """A captured graph holds these addresses; raise if any of them has changed since construction."""
@@ -339,7 +347,8 @@ class FusedTPPlan:
                                 e_score_correction_bias, tp_mc_ptr=self.pool.mc_ptr(slot),
                                 tp_pads_ptr=self.pool.pads_ptr, tp_seqctr_ptr=self.pool.seqctr_ptr,
                                 tp_rank=self.rank, tp_world=self.world, tp_nchunk=nchunk, tp_ncomm=self.ncomm,
-                                tp_residual=residual, tp_out_scale=out_scale, check=check, expert_map=expert_map)
+                                tp_residual=residual, tp_out_scale=out_scale, check=check, expert_map=expert_map,
+                                tp_peers_ptr=self.pool.peers_ptr(slot) if self.world == PEER_REDUCE_WORLD else 0)
         return out
 
 
