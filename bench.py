@@ -752,8 +752,9 @@ def verify_reduced_output(spec, mk, layer, batch, emap, sc, pool_plan, result, w
                           fused) -> dict:
     """Before anything is timed on N > 1 GPUs: the reduced output of the configuration that is about to be
     timed (`result`, left there by the warm-up steps) must
-      * when the reduce ran inside the kernel: equal an ordinary launch followed by torch's multimem
-        all-reduce bit for bit (both sum in fp32 inside the switch and round once),
+      * when the reduce ran inside the kernel: equal, bit for bit, an ordinary launch followed by torch's multimem
+        all-reduce (the same in-switch reduction) or, with two ranks, by the correctly rounded fp32 sum of the
+        two copies (what the peer-load reduce forms),
       * agree with an ordinary launch + NCCL all-reduce (ulp statistics reported, the largest difference
         bounded against the output's rms: NCCL may sum in another order and round between hops),
       * match the CPU oracle on sampled tokens within the layer's tolerance (rank 0 evaluates every rank's shard).
@@ -768,12 +769,20 @@ def verify_reduced_output(spec, mk, layer, batch, emap, sc, pool_plan, result, w
     if pool_plan is not None:
         view = pool_plan.pool.output(T, 1)
         view.copy_(plain)
-        torch.ops.symm_mem.multimem_all_reduce_(view, "sum", dist.group.WORLD.group_name)
+        if world == tp_fused.PEER_REDUCE_WORLD:
+            # two ranks: the kernel reads the peer's copy directly and forms the correctly rounded fp32 sum
+            # (the in-switch reduction rounds ties differently)
+            parts = [torch.empty_like(plain) for _ in range(world)]
+            dist.all_gather(parts, plain)
+            view.copy_((parts[0].float() + parts[1].float()).to(torch.bfloat16))
+            key = "bitwise_equal_to_kernel_plus_correctly_rounded_sum"
+        else:
+            torch.ops.symm_mem.multimem_all_reduce_(view, "sum", dist.group.WORLD.group_name)
+            key = "bitwise_equal_to_kernel_plus_multimem_all_reduce"
         torch.cuda.synchronize()
-        info["bitwise_equal_to_kernel_plus_multimem_all_reduce"] = bool(
-            torch.equal(got.view(torch.int16), view.view(torch.int16)))
+        info[key] = bool(torch.equal(got.view(torch.int16), view.view(torch.int16)))
         if fused:
-            ok = ok and info["bitwise_equal_to_kernel_plus_multimem_all_reduce"]
+            ok = ok and info[key]
     dist.all_reduce(plain)
     d = (_bf16_order_key(got) - _bf16_order_key(plain)).abs()
     rms = float(plain.float().pow(2).mean().sqrt())

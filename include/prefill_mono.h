@@ -157,8 +157,8 @@ int prefill_wgmma_shm_total(void);            /* Q:1789 */
 /* launch_prefill_moe_wgmma_q1_ep2 plus tp_peers: a device array of tp_world pointers, every rank's address of the
  * output window (the reference's symmetric pool exposes the same table, fused_moe/symm_output_pool.py:95-149; its
  * kernel does not use it). With two ranks the in-kernel reduce then reads the peer's copy directly over NVLink,
- * adds its own copy from local memory and writes the sum to both ranks: the same bits as the multicast reduce for a
- * third of the link traffic (through the multicast alias the switch fetches this rank's own copy over NVLink too).
+ * adds its own copy from local memory and writes the sum to both ranks: the same bits as the multicast reduce for two
+ * thirds of the link traffic (through the multicast alias the switch fetches this rank's own copy over NVLink too).
  * With more ranks, or a null table, it behaves exactly like the _ep2 entry. */
 int prefill_wgmma_tp_has_peer_reduce(void);   /* 1 = launch_prefill_moe_wgmma_q1_ep3 is usable */
 int launch_prefill_moe_wgmma_q1_ep3(const float* logits, int num_tokens, int block_m, void* workspace,

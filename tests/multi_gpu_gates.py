@@ -9,6 +9,7 @@ leaves that reduce to the caller). Launch with torchrun, one rank per GPU:
 Gates per (token count, ncomm); every rank must agree:
   g1  the fused entry with ncomm = 0 is bitwise the ordinary kernel                 (tp8_fuse_ab.py:314-323)
   g2  reduce inside the kernel == ordinary kernel + multimem all-reduce, bitwise     (tp8_fuse_ab.py:391-405)
+      (two ranks: == the correctly rounded fp32 sum of the two copies, which is what the peer-load reduce forms)
   g3  NCCL all-reduce against the multimem all-reduce, in bf16 ulps (reported)       (tp8_fuse_ab.py:119-124)
   g4  fold: scale 0 returns the reduced residual; 2.5 * routed + residual bitwise == the same fold by the
       ordinary kernel + multimem all-reduce                                          (tp8_fold_gate.py:332-409)
@@ -134,12 +135,25 @@ class Rig:
     def status(self, T):
         self.mk.check_status(self.mk.scratch(T, self.dev)["workspace"])
 
+    def all_reduce_like_the_kernel(self, view):
+        """The all-reduce the in-kernel reduce must reproduce bit for bit, applied in place to a pool view.
+        More than two ranks: torch's multimem all-reduce (the same in-switch reduction). Two ranks: the kernel
+        reads the peer's copy directly and adds in fp32 with one round-to-nearest-even, which for two summands is
+        THE correctly rounded sum -- computed here from the gathered copies (the switch rounds ties differently:
+        its result and NCCL's differ in the last bit of about every sixth element)."""
+        if self.world == tp_fused.PEER_REDUCE_WORLD:
+            parts = [torch.empty_like(view) for _ in range(self.world)]
+            dist.all_gather(parts, view.contiguous())
+            view.copy_((parts[0].float() + parts[1].float()).to(torch.bfloat16))
+        else:
+            torch.ops.symm_mem.multimem_all_reduce_(view, "sum", self.gname)
+        torch.cuda.synchronize()
+
     def reference(self, T, slot=0):
-        """Ordinary kernel into the pool view, then torch's multimem all-reduce: what the fused launch must equal."""
+        """Ordinary kernel into the pool view, then the all-reduce: what the fused launch must equal."""
         view = self.plan.pool.output(T, slot)
         self.raw(T, view)
-        torch.ops.symm_mem.multimem_all_reduce_(view, "sum", self.gname)
-        torch.cuda.synchronize()
+        self.all_reduce_like_the_kernel(view)
         return view.clone()
 
     def all_agree(self, ok: bool) -> bool:
@@ -170,12 +184,17 @@ def gates_for(rig: Rig, T: int, ncomm: int) -> dict:
     rig.raw(T, pool_view)
     r["g1_ncomm0_inert"] = same_bits(out_plain, pool_view)
     # references
-    torch.ops.symm_mem.multimem_all_reduce_(pool_view, "sum", rig.gname)
-    torch.cuda.synchronize()
+    multimem = pool_view.clone()
+    rig.all_reduce_like_the_kernel(pool_view)
     ref = pool_view.clone()
     nccl = out_plain.clone()
     dist.all_reduce(nccl)
-    r["g3_nccl_vs_multimem"] = ulpstats(nccl, ref)
+    symm_view = plan.pool.output(T, 1)
+    symm_view.copy_(multimem)
+    torch.ops.symm_mem.multimem_all_reduce_(symm_view, "sum", rig.gname)
+    torch.cuda.synchronize()
+    r["g3_nccl_vs_multimem"] = ulpstats(nccl, symm_view)
+    r["g3_reference_vs_nccl"] = ulpstats(ref, nccl)
     # g2
     pool_view.zero_()
     got = rig.fused(T, C, ncomm, check=True)
@@ -220,12 +239,10 @@ def gates_for(rig: Rig, T: int, ncomm: int) -> dict:
         resid = (torch.randn(T, spec.hidden, device=dev, generator=gen) * 0.05).to(torch.bfloat16)
         got0 = rig.fused(T, C, ncomm, residual=resid, scale=0.0, check=True).clone()
         pool_view.copy_(resid)
-        torch.ops.symm_mem.multimem_all_reduce_(pool_view, "sum", rig.gname)
-        torch.cuda.synchronize()
+        rig.all_reduce_like_the_kernel(pool_view)
         r["g4_scale0_is_reduced_residual"] = same_bits(got0, pool_view)
         rig.raw(T, pool_view, resid, 2.5)
-        torch.ops.symm_mem.multimem_all_reduce_(pool_view, "sum", rig.gname)
-        torch.cuda.synchronize()
+        rig.all_reduce_like_the_kernel(pool_view)
         ref_fold = pool_view.clone()
         gotf = rig.fused(T, C, ncomm, residual=resid, scale=2.5, check=True)
         torch.cuda.synchronize()

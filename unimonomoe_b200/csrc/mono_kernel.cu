@@ -1593,8 +1593,10 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         bool live[UN];
         if (peer_pair != nullptr) {
           // Two ranks: read the peer's copy over NVLink, add this rank's own copy from local memory, write the
-          // sum to both. The multicast form makes the switch fetch BOTH copies over NVLink (this rank's too) and
-          // deliver the result twice: three times the link traffic of this form for the same bits.
+          // sum to both. Per GPU and direction that moves the output once (half read by the peer, half written to
+          // it); the multicast form makes the switch fetch this rank's own copy over NVLink as well and deliver
+          // the result to both: one and a half times the traffic for the same bits. (From three ranks on the
+          // in-switch reduction and multicast store move less than peer loads and stores would.)
           uint32_t y[UN][4];
 #pragma unroll
           for (int u = 0; u < UN; ++u) {
@@ -2151,7 +2153,7 @@ int launch_prefill_moe_wgmma_q1_ep2(const float* logits, int num_tokens, int blo
 
 // The _ep2 entry plus tp_peers: a device array of tp_world pointers, every rank's address of the output window
 // (bf16_output on that rank). With two ranks the in-kernel reduce then reads the peer's copy directly instead
-// of going through the multicast alias (a third of the NVLink traffic, the same bits); with more ranks, or a null
+// of going through the multicast alias (two thirds of the NVLink traffic, the same bits); with more ranks, or a null
 // table, it is the multicast reduce of the _ep2 entry.
 int prefill_wgmma_tp_has_peer_reduce() { return 1; }
 int launch_prefill_moe_wgmma_q1_ep3(const float* logits, int num_tokens, int block_m, void* workspace,

@@ -45,7 +45,8 @@ FUSED_CHUNKS_BY_TOKENS = {8192: 4, 16384: 8}
 # Communication CTAs. The reference settled on 14 of its 132 (monokernel_tp.py:87).
 FUSED_NCOMM = 14
 # Group size at which the kernel reduces by direct peer loads instead of the multicast alias: with two ranks the
-# switch would fetch this rank's own copy over NVLink as well, three times the traffic for the same bits.
+# switch would fetch this rank's own copy over NVLink as well, one and a half times the traffic for the same bits.
+# From three ranks on the in-switch reduction moves less than peer loads would.
 PEER_REDUCE_WORLD = 2
 
 
