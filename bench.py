@@ -451,12 +451,16 @@ def stall_counters(mk, workspace) -> None:
     off = mk._int_symbol("prof_offset")
     if off is None:
         return
-    pr = workspace.cpu()[off: off + 148 * 16 * 8].view(torch.int64).view(148, 16).double()
+    pr = workspace.cpu()[off: off + 148 * 64 * 8].view(torch.int64).view(148, 64).double()
     if float(pr.sum()) == 0.0:
         return
     print("# stall counters of the last launch, mean over CTAs, kcycles: " +
           ", ".join(f"{n}={pr[:, i].mean().item() / 1e3:.1f}" for i, n in enumerate(PROF_NAMES) if n != "-"),
           file=sys.stderr)
+    for row, who in ((16, "epilogue waiting for a full accumulator"), (40, "MMA thread waiting for a free accumulator")):
+        h = pr[:, row: row + 24].mean(0) / 1e3
+        print(f"# {who}, kcycles by slab of the pass: up " + " ".join(f"{v:.1f}" for v in h[:16].tolist())
+              + " | down " + " ".join(f"{v:.1f}" for v in h[16:20].tolist()), file=sys.stderr)
 
 
 def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barrier, dev, with_logits=True,

@@ -7,6 +7,9 @@
 // (kernel/moe_monokernel/src/moe_grid_barrier.h:101-199,
 // kernel/qwen_tp/src/prefill_mono_final_nb.cu:244-247, :1468, :1500).
 #pragma once
+#ifndef MONO_LAZYWAIT
+#define MONO_LAZYWAIT 0
+#endif
 #include <cstddef>
 #include <cstdint>
 #include "ptx_sm100.cuh"
@@ -51,7 +54,7 @@ struct Workspace {
   int32_t reserved1[3];
   int32_t cta_hist[kGrid][kNumExperts];     // per-CTA histograms (basis of the stable scatter)
   uint64_t phase_ns[8];                     // %globaltimer at phase boundaries, written by block 0
-  uint64_t prof[kGrid][16];                 // per-CTA stall counters (cycles), filled only by MONO_PROFILE builds
+  uint64_t prof[kGrid][64];                 // per-CTA stall counters (cycles), filled only by MONO_PROFILE builds
 };
 constexpr size_t kWorkspaceZeroBytes = offsetof(Workspace, total_tiles);
 
@@ -75,6 +78,24 @@ __device__ __forceinline__ bool aborted(const Workspace* ws) { return ld_relaxed
 
 // Wait for phase `parity` of a shared-memory barrier. False on abort or time-out.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& c, uint32_t site) {
+#if MONO_LAZYWAIT
+  // the clock and the abort flag (a load from L2) are looked at every 256th poll only: in a healthy
+  // launch a wait ends long before, and nothing slow sits between two polls
+  uint64_t t0 = 0;
+  uint32_t polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 255u) == 0u) {
+      if (aborted(c.ws)) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > c.timeout_ns) {
+        report_error(c.ws, kErrMbarrier, site, parity, threadIdx.x);
+        return false;
+      }
+    }
+  }
+  return true;
+#else
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t polls = 0;
@@ -88,6 +109,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     }
   }
   return true;
+#endif
 }
 
 // Spin until *p >= target (device scope). False on abort or time-out.

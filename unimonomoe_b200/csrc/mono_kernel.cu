@@ -65,6 +65,10 @@
 #define MONO_ROUTER_MODE 0
 #endif
 
+#ifndef MONO_LDPIPE
+#define MONO_LDPIPE 0
+#endif
+
 // Development only: MONO_ABLATE is a bit mask that removes a piece of the epilogue's work (the
 // results are then wrong) so that its share of the run time can be measured by difference.
 //   1: no TMEM read-out / promotion   2: no SiLU / requantisation arithmetic   4: no partial-row stores
@@ -78,11 +82,13 @@
 #define PROF_T0() const long long prof_t0_ = clock64()
 #define PROF_ADD(n) n += clock64() - prof_t0_
 #define PROF_STORE(slot, n) p.ws->prof[blockIdx.x][slot] = static_cast<uint64_t>(n)
+#define PROF_HIST(row, bin, who) do { if (who) S.whist[row][bin] += static_cast<unsigned long long>(clock64() - prof_t0_); } while (0)
 #else
 #define PROF_DECL(n)
 #define PROF_T0()
 #define PROF_ADD(n)
 #define PROF_STORE(slot, n)
+#define PROF_HIST(row, bin, who)
 #endif
 
 namespace mono {
@@ -196,7 +202,10 @@ static_assert(NWARPS * E * 4 <= SA * A_STAGE_BYTES, "phase-0 histograms live in 
 // hardware hands out only what this CTA released, and setmaxnreg.inc waits (without a bound)
 // until it is available, so the three counts MUST satisfy the inequality below.
 constexpr int REGS_LAUNCH = (65536 / BLOCK) / 8 * 8;            // 168 at 384 threads, 96 at 640
-constexpr int REGS_PRODUCER = (EPI_WGS == 2) ? 56 : 40;
+#ifndef MONO_REGS_PRODUCER
+#define MONO_REGS_PRODUCER 56
+#endif
+constexpr int REGS_PRODUCER = (EPI_WGS == 2) ? MONO_REGS_PRODUCER : 40;
 constexpr int REGS_EPILOGUE = ((BLOCK * REGS_LAUNCH - 128 * REGS_PRODUCER) / N_EPI) / 8 * 8;  // 224 / 104
 static_assert(128 * REGS_PRODUCER + N_EPI * REGS_EPILOGUE <= BLOCK * REGS_LAUNCH,
               "setmaxnreg.inc would wait forever: the epilogue asks for more registers than the producers release");
@@ -546,6 +555,11 @@ struct __align__(16) SharedState {
   TileInfo tiles[MAX_MY_TILES];
   float rowmax[2][EPI_WGS][TILE_M];
   alignas(16) int gather_tok[2][8][TILE_M / 8];  // token of row gr + 8 i of the tile being gathered, [tile parity][gr][i]
+#ifdef MONO_PROFILE
+  // wait cycles by position of the slab step inside its pass: [0,16) up-projection slab ks, [16,20) down-projection slab dk;
+  // one row for the epilogue's waits for a full accumulator, one for the MMA thread's waits for a free one
+  unsigned long long whist[2][24];
+#endif
 };
 static_assert(sizeof(SharedState) <= SMEM_STATIC_RESERVE, "static shared state exceeds its reserve");
 
@@ -926,6 +940,9 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
     }
     for (int s = 0; s < SB; ++s) { mbar_init(&S.fullB[s], 1); mbar_init(&S.emptyB[s], 1); }
     for (int s = 0; s < NBUF; ++s) { mbar_init(&S.tmem_full[s], 1); mbar_init(&S.tmem_empty[s], both * (N_EPI / 32)); }
+#ifdef MONO_PROFILE
+    for (int i = 0; i < 48; ++i) (&S.whist[0][0])[i] = 0ull;
+#endif
     for (int s = 0; s < NP; ++s) mbar_init(&S.inter_ready[s], both * (N_EPI / 32));
     mbar_init_fence();
   }
@@ -1069,7 +1086,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               const uint32_t buf = nt % NBUF;
               { PROF_T0();
               if (!mbar_wait(&S.tmem_empty[buf], ((nt / NBUF) & 1u) ^ 1u, wc, kSiteTmemEmpty)) { ok = false; break; }
-              PROF_ADD(pm_tmem); }
+              PROF_ADD(pm_tmem); PROF_HIST(1, ((s % NK) < 16 ? (s % NK) : 15), true); }
               tc_fence_after();
               const uint64_t db = umma_desc_sw128(b_ring_u32 + sb * B_STAGE_BYTES + j * BC * 128);
               const uint32_t d = tmem_base + buf * BC;
@@ -1110,7 +1127,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               const uint32_t buf = nt % NBUF;
               { PROF_T0();
               if (!mbar_wait(&S.tmem_empty[buf], ((nt / NBUF) & 1u) ^ 1u, wc, kSiteTmemEmpty)) { ok = false; break; }
-              PROF_ADD(pm_tmem); }
+              PROF_ADD(pm_tmem); PROF_HIST(1, 16 + dk, true); }
               tc_fence_after();
               const uint64_t db = umma_desc_sw128(b_ring_u32 + sb * B_STAGE_BYTES + j * BC * 128);
               const uint32_t d = tmem_base + buf * BC;
@@ -1135,6 +1152,9 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
 #endif
         PROF_STORE(1, pm_fullB); PROF_STORE(2, pm_fullA); PROF_STORE(3, pm_tmem); PROF_STORE(4, pm_inter);
         PROF_STORE(5, pm_total);
+#ifdef MONO_PROFILE
+        for (int i = 0; i < 24; ++i) p.ws->prof[blockIdx.x][40 + i] = S.whist[1][i];
+#endif
       }
     } else {
       // ---------------------------------------------------------- activation gather (warps 2-3, 64 threads)
@@ -1230,6 +1250,34 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
           if (lane == 0) { if (PAIR && !leader) mbar_arrive_cluster(at_leader(&S.tmem_empty[buf])); else mbar_arrive(&S.tmem_empty[buf]); }
           return;
         }
+#if MONO_LDPIPE
+        // pieces of MONO_LDPIPE columns, the next piece in flight while this one is folded
+        {
+          constexpr int PW = MONO_LDPIPE, NPC = WC / PW;
+          uint32_t va[PW], vb[PW];
+          tmem_ld_n<PW>(t_lane + buf * BC, va);
+#pragma unroll
+          for (int c = 0; c < NPC; ++c) {
+            uint32_t (&cur)[PW] = (c & 1) ? vb : va;
+            uint32_t (&nxt)[PW] = (c & 1) ? va : vb;
+            tmem_ld_wait();
+            if (c + 1 < NPC) tmem_ld_n<PW>(t_lane + buf * BC + (c + 1) * PW, nxt);
+            if (c == NPC - 1) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) { if (PAIR && !leader) mbar_arrive_cluster(at_leader(&S.tmem_empty[buf])); else mbar_arrive(&S.tmem_empty[buf]); }
+            }
+#pragma unroll
+            for (int i = 0; i < PW / 2; ++i) {
+              const int pair = c * (PW / 2) + i;
+              const float sc = (pair < HCB / 2) ? s_lo : s_hi;
+              acc[j * (WC / 2) + pair] = __ffma2_rn(make_float2(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1])),
+                                                    make_float2(sc, sc), acc[j * (WC / 2) + pair]);
+            }
+          }
+          return;
+        }
+#endif
 #pragma unroll
         for (int c = 0; c < NLD; ++c) {
           uint32_t v[LDW];
@@ -1344,7 +1392,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               const uint32_t buf = nt % NBUF;
               { PROF_T0();
               if (!dead && !mbar_wait(&S.tmem_full[buf], (nt / NBUF) & 1u, wc, kSiteTmemFull)) dead = true;
-              PROF_ADD(pe_wait); }
+              PROF_ADD(pe_wait); PROF_HIST(0, (ks < 16 ? ks : 15), et == 0); }
               PROF_T0();
               if (!dead) promote(j, buf, s_g, s_u);
               PROF_ADD(pe_up);
@@ -1439,7 +1487,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               const uint32_t buf = nt % NBUF;
               { PROF_T0();
               if (!dead && !mbar_wait(&S.tmem_full[buf], (nt / NBUF) & 1u, wc, kSiteTmemFull)) dead = true;
-              PROF_ADD(pe_wait); }
+              PROF_ADD(pe_wait); PROF_HIST(0, 16 + dk, et == 0); }
               PROF_T0();
               if (!dead) promote(j, buf, sc, sc);
               PROF_ADD(pe_down);
@@ -1492,6 +1540,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         PROF_STORE(12, pe_store); PROF_STORE(14, pe_bar);
 #ifdef MONO_PROFILE
         p.ws->prof[blockIdx.x][13] = static_cast<uint64_t>(clock64() - pe_start);
+        for (int i = 0; i < 24; ++i) p.ws->prof[blockIdx.x][16 + i] = S.whist[0][i];
 #endif
       }
     }
