@@ -451,7 +451,10 @@ def stall_counters(mk, workspace) -> None:
     off = mk._int_symbol("prof_offset")
     if off is None:
         return
-    pr = workspace.cpu()[off: off + 148 * 64 * 8].view(torch.int64).view(148, 64).double()
+    raw = workspace.cpu()[off: off + 148 * 64 * 8]
+    if raw.numel() != 148 * 64 * 8:
+        return
+    pr = raw.view(torch.int64).view(148, 64).double()
     if float(pr.sum()) == 0.0:
         return
     print("# stall counters of the last launch, mean over CTAs, kcycles: " +

@@ -50,14 +50,8 @@ VARIANTS = {
 # expert phase out (wrong results by design; their run-time differences split the phase)
 DEV_VARIANTS = {
     "qwen_w1_prof": dict(QWEN, N_HALF=512, E_LOCAL=256, PROFILE=1),
-    "qwen_w1_x1": dict(QWEN, N_HALF=512, E_LOCAL=256, DEFS=("MONO_LDPIPE=32",)),
-    "qwen_w1_x2": dict(QWEN, N_HALF=512, E_LOCAL=256, DEFS=("MONO_LAZYWAIT=1",)),
-    "qwen_w1_x3": dict(QWEN, N_HALF=512, E_LOCAL=256, DEFS=("MONO_LDPIPE=32", "MONO_LAZYWAIT=1")),
-    "qwen_w1_x4": dict(QWEN, N_HALF=512, E_LOCAL=256, DEFS=("MONO_LDPIPE=32", "MONO_LAZYWAIT=1", "MONO_REGS_PRODUCER=40")),
-    "qwen_w1_x5": dict(QWEN, N_HALF=512, E_LOCAL=256, DEFS=("MONO_LDPIPE=16", "MONO_LAZYWAIT=1")),
-    "qwen_w1_x5_prof": dict(QWEN, N_HALF=512, E_LOCAL=256, PROFILE=1, DEFS=("MONO_LDPIPE=16", "MONO_LAZYWAIT=1")),
-    "qwen_w1_x3_prof": dict(QWEN, N_HALF=512, E_LOCAL=256, PROFILE=1, DEFS=("MONO_LDPIPE=32", "MONO_LAZYWAIT=1")),
-    **{f"qwen_w1_abl{m}": dict(QWEN, N_HALF=512, E_LOCAL=256, ABLATE=m) for m in (1, 4, 7, 23, 31)},
+    "qwen_w1_trace": dict(QWEN, N_HALF=512, E_LOCAL=256, PROFILE=1, DEFS=("MONO_TRACE",)),
+    **{f"qwen_w1_abl{m}": dict(QWEN, N_HALF=512, E_LOCAL=256, ABLATE=m) for m in (1, 4, 7, 23, 31, 39, 71)},
 }
 
 SOURCES = ["mono_kernel.cu", "ptx_sm100.cuh", "pair_sm100.cuh", "bounded_wait.cuh", "route_math.cuh"]

@@ -7,9 +7,6 @@
 // (kernel/moe_monokernel/src/moe_grid_barrier.h:101-199,
 // kernel/qwen_tp/src/prefill_mono_final_nb.cu:244-247, :1468, :1500).
 #pragma once
-#ifndef MONO_LAZYWAIT
-#define MONO_LAZYWAIT 0
-#endif
 #include <cstddef>
 #include <cstdint>
 #include "ptx_sm100.cuh"
@@ -78,24 +75,6 @@ __device__ __forceinline__ bool aborted(const Workspace* ws) { return ld_relaxed
 
 // Wait for phase `parity` of a shared-memory barrier. False on abort or time-out.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& c, uint32_t site) {
-#if MONO_LAZYWAIT
-  // the clock and the abort flag (a load from L2) are looked at every 256th poll only: in a healthy
-  // launch a wait ends long before, and nothing slow sits between two polls
-  uint64_t t0 = 0;
-  uint32_t polls = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++polls & 255u) == 0u) {
-      if (aborted(c.ws)) return false;
-      const uint64_t now = globaltimer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > c.timeout_ns) {
-        report_error(c.ws, kErrMbarrier, site, parity, threadIdx.x);
-        return false;
-      }
-    }
-  }
-  return true;
-#else
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t polls = 0;
@@ -109,7 +88,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     }
   }
   return true;
-#endif
+}
+
+// The same wait made by all 32 lanes of a converged warp with a warp-uniform result, so that the code after it
+// stays convergent (the MMA warp: its tcgen05 instructions are issued by an elected lane out of uniform control
+// flow, which lets the compiler keep descriptors and addresses in uniform registers).
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const WaitCtx& c, uint32_t site) {
+  if (__all_sync(0xFFFFFFFFu, mbar_try_wait(bar, parity))) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t polls = 0;
+  while (!__all_sync(0xFFFFFFFFu, mbar_try_wait(bar, parity))) {
+    if ((++polls & 31u) == 0u) {
+      bool bad = false;
+      if ((threadIdx.x & 31u) == 0u) {
+        if (aborted(c.ws)) bad = true;
+        else if (globaltimer_ns() - t0 > c.timeout_ns) {
+          report_error(c.ws, kErrMbarrier, site, parity, threadIdx.x);
+          bad = true;
+        }
+      }
+      if (__any_sync(0xFFFFFFFFu, bad)) return false;
+    }
+  }
+  return true;
 }
 
 // Spin until *p >= target (device scope). False on abort or time-out.

@@ -65,23 +65,39 @@
 #define MONO_ROUTER_MODE 0
 #endif
 
-#ifndef MONO_LDPIPE
-#define MONO_LDPIPE 0
-#endif
-
 // Development only: MONO_ABLATE is a bit mask that removes a piece of the epilogue's work (the
 // results are then wrong) so that its share of the run time can be measured by difference.
 //   1: no TMEM read-out / promotion   2: no SiLU / requantisation arithmetic   4: no partial-row stores
 //   8: no activation gather copies    16: no weight TMA loads
+//   64: no operand hand-shake at all (producers idle; the MMA warp waits only for accumulator buffers)
+//   32: the intermediate's passes alias one 16 KB slot, which leaves room for four-deep operand rings
 #ifndef MONO_ABLATE
 #define MONO_ABLATE 0
+#endif
+#ifndef MONO_MMA_WARP
+#define MONO_MMA_WARP 1
+#endif
+
+// Development only: MONO_TRACE (with MONO_PROFILE) makes CTA 0 write clock64 time stamps of its MMA thread
+// (5 per slab step: top, operands B, operands A, accumulator free, issued) and of epilogue thread 0 (4 per step:
+// before the wait, after it, buffer released, folded) over the stall-counter area, for a timeline of the hand-shake.
+#if defined(MONO_TRACE) && defined(MONO_PROFILE)
+#define TRACE_M(k) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && tr_m < 4000) reinterpret_cast<unsigned long long*>(p.ws->prof)[tr_m++] = clock64(); } while (0)
+#define TRACE_E(k) do { if (blockIdx.x == 0 && et == 0 && tr_e < 8000) reinterpret_cast<unsigned long long*>(p.ws->prof)[tr_e++] = clock64(); } while (0)
+#else
+#define TRACE_M(k)
+#define TRACE_E(k)
 #endif
 
 #ifdef MONO_PROFILE
 #define PROF_DECL(n) long long n = 0
 #define PROF_T0() const long long prof_t0_ = clock64()
 #define PROF_ADD(n) n += clock64() - prof_t0_
+#ifdef MONO_TRACE
+#define PROF_STORE(slot, n)
+#else
 #define PROF_STORE(slot, n) p.ws->prof[blockIdx.x][slot] = static_cast<uint64_t>(n)
+#endif
 #define PROF_HIST(row, bin, who) do { if (who) S.whist[row][bin] += static_cast<unsigned long long>(clock64() - prof_t0_); } while (0)
 #else
 #define PROF_DECL(n)
@@ -177,7 +193,8 @@ constexpr int A_STAGE_BYTES = TILE_M * 128;  // 128 rows x 128 B
 constexpr int B_ROWS = PAIR ? 128 : 256;     // weight rows of a stage kept by one CTA
 constexpr int B_STAGE_BYTES = B_ROWS * 128;  // x 128 B
 constexpr int STAGE_CAP = PAIR ? 6 : 4;
-constexpr int INTER_BYTES = NP * A_STAGE_BYTES;
+constexpr int INTER_SLOTS = (MONO_ABLATE & 32) ? 1 : NP;  // ablation 32: all passes share one slot (deeper rings, wrong results)
+constexpr int INTER_BYTES = INTER_SLOTS * A_STAGE_BYTES;
 constexpr int SMEM_CAP = 227 * 1024;
 constexpr int SMEM_STATIC_RESERVE = 6 * 1024;
 // per-tile scale staging: activation scales [NK][128], and (double buffered) the expert's
@@ -976,7 +993,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         uint32_t nb = 0;
         bool ok = true;
         PROF_DECL(pw_emptyB);
-        for (int it = 0; it < n_my && ok; ++it) {
+        for (int it = 0; it < ((MONO_ABLATE & 64) ? 0 : n_my) && ok; ++it) {
           const int ch = S.tiles[it].chunk;
           const bool sh = S.tiles[it].e == SHARED_E;
           const int e = sh ? 0 : S.tiles[it].e;                     // row base inside the weight tensor
@@ -1061,9 +1078,24 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             }
           }
         }
-      } else if (lane == 0) {
+      } else if (MONO_MMA_WARP != 0 || lane == 0) {
+        // MONO_MMA_WARP: the whole warp walks the loop in uniform control flow and waits together; an elected lane
+        // issues the tcgen05 instructions. With a single lane in a divergent branch instead, every descriptor and
+        // address has to be moved into a uniform register per instruction, and the seven tcgen05 instructions of a
+        // slab step then take longer to issue than the tensor core takes to execute them.
+        auto wait_bar = [&](uint64_t* bar, uint32_t parity, uint32_t site) -> bool {
+          if constexpr (MONO_MMA_WARP != 0) return mbar_wait_warp(bar, parity, wc, site);
+          else return mbar_wait(bar, parity, wc, site);
+        };
+        auto issuer = [&]() -> bool {
+          if constexpr (MONO_MMA_WARP != 0) return elect_one_sync();
+          else return true;
+        };
         uint32_t nb = 0, na = 0, nt = 0;
         bool ok = true;
+#if defined(MONO_TRACE) && defined(MONO_PROFILE)
+        int tr_m = 0;
+#endif
         PROF_DECL(pm_fullB); PROF_DECL(pm_fullA); PROF_DECL(pm_tmem); PROF_DECL(pm_inter); PROF_DECL(pm_total);
 #ifdef MONO_PROFILE
         const long long pm_start = clock64();
@@ -1072,12 +1104,15 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
         for (int it = 0; it < n_my && ok; ++it) {
           for (int s = 0; s < NP * NK; ++s) {
             const uint32_t sb = nb % SB, sa = na % SA;
+            TRACE_M(0);
             { PROF_T0();
-            if (!mbar_wait(&S.fullB[sb], (nb / SB) & 1u, wc, kSiteFullB)) { ok = false; break; }
+            if ((MONO_ABLATE & 64) == 0 && !wait_bar(&S.fullB[sb], (nb / SB) & 1u, kSiteFullB)) { ok = false; break; }
             PROF_ADD(pm_fullB); }
+            TRACE_M(1);
             { PROF_T0();
-            if (!mbar_wait(&S.fullA[sa], (na / SA) & 1u, wc, kSiteFullA)) { ok = false; break; }
+            if ((MONO_ABLATE & 64) == 0 && !wait_bar(&S.fullA[sa], (na / SA) & 1u, kSiteFullA)) { ok = false; break; }
             PROF_ADD(pm_fullA); }
+            TRACE_M(2);
             // the gathered rows were written by cp.async (generic proxy); the tensor core reads them through the async proxy
             fence_proxy_async_smem();
             const uint64_t da = umma_desc_sw128(a_ring_u32 + sa * A_STAGE_BYTES);
@@ -1085,26 +1120,34 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             for (int j = 0; j < NSPLIT; ++j) {
               const uint32_t buf = nt % NBUF;
               { PROF_T0();
-              if (!mbar_wait(&S.tmem_empty[buf], ((nt / NBUF) & 1u) ^ 1u, wc, kSiteTmemEmpty)) { ok = false; break; }
-              PROF_ADD(pm_tmem); PROF_HIST(1, ((s % NK) < 16 ? (s % NK) : 15), true); }
+              if (!wait_bar(&S.tmem_empty[buf], ((nt / NBUF) & 1u) ^ 1u, kSiteTmemEmpty)) { ok = false; break; }
+              PROF_ADD(pm_tmem); PROF_HIST(1, ((s % NK) < 16 ? (s % NK) : 15), lane == 0); }
+              TRACE_M(3);
               tc_fence_after();
               const uint64_t db = umma_desc_sw128(b_ring_u32 + sb * B_STAGE_BYTES + j * BC * 128);
               const uint32_t d = tmem_base + buf * BC;
-              if constexpr (PAIR) {
+              if (issuer()) {
+                if constexpr (PAIR) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_f8_pair(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
-                umma_commit_pair(&S.tmem_full[buf]);
-              } else {
+                  for (int k = 0; k < 4; ++k) umma_f8_pair(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+                  umma_commit_pair(&S.tmem_full[buf]);
+                } else {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
-                umma_commit(&S.tmem_full[buf]);
+                  for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+                  umma_commit(&S.tmem_full[buf]);
+                }
               }
+              if constexpr (MONO_MMA_WARP != 0) __syncwarp();
               ++nt;
             }
             if (!ok) break;
-            if constexpr (PAIR) { umma_commit_pair(&S.emptyA[sa]); umma_commit_pair(&S.emptyB[sb]); }
-            else { umma_commit(&S.emptyA[sa]); umma_commit(&S.emptyB[sb]); }
+            if ((MONO_ABLATE & 64) == 0 && issuer()) {
+              if constexpr (PAIR) { umma_commit_pair(&S.emptyA[sa]); umma_commit_pair(&S.emptyB[sb]); }
+              else { umma_commit(&S.emptyA[sa]); umma_commit(&S.emptyB[sb]); }
+            }
+            if constexpr (MONO_MMA_WARP != 0) __syncwarp();
             ++nb; ++na;
+            TRACE_M(4);
           }
           if (!ok) break;
           for (int s = 0; s < NHB * NP; ++s) {
@@ -1114,46 +1157,57 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               // K slab dk of the down projection reads the 128 intermediate columns pass dk wrote: the first
               // slabs start while the epilogue is still in the SiLU section of the last pass
               { PROF_T0();
-              if (!mbar_wait(&S.inter_ready[dk], static_cast<uint32_t>(it) & 1u, wc, kSiteInterReady)) { ok = false; break; }
+              if (!wait_bar(&S.inter_ready[dk], static_cast<uint32_t>(it) & 1u, kSiteInterReady)) { ok = false; break; }
               PROF_ADD(pm_inter); }
               tc_fence_after();
             }
+            TRACE_M(0);
             { PROF_T0();
-            if (!mbar_wait(&S.fullB[sb], (nb / SB) & 1u, wc, kSiteFullB)) { ok = false; break; }
+            if ((MONO_ABLATE & 64) == 0 && !wait_bar(&S.fullB[sb], (nb / SB) & 1u, kSiteFullB)) { ok = false; break; }
             PROF_ADD(pm_fullB); }
-            const uint64_t da = umma_desc_sw128(inter_u32 + dk * A_STAGE_BYTES);
+            TRACE_M(1);
+            TRACE_M(2);
+            const uint64_t da = umma_desc_sw128(inter_u32 + (dk % INTER_SLOTS) * A_STAGE_BYTES);
 #pragma unroll
             for (int j = 0; j < NSPLIT; ++j) {
               const uint32_t buf = nt % NBUF;
               { PROF_T0();
-              if (!mbar_wait(&S.tmem_empty[buf], ((nt / NBUF) & 1u) ^ 1u, wc, kSiteTmemEmpty)) { ok = false; break; }
-              PROF_ADD(pm_tmem); PROF_HIST(1, 16 + dk, true); }
+              if (!wait_bar(&S.tmem_empty[buf], ((nt / NBUF) & 1u) ^ 1u, kSiteTmemEmpty)) { ok = false; break; }
+              PROF_ADD(pm_tmem); PROF_HIST(1, 16 + dk, lane == 0); }
+              TRACE_M(3);
               tc_fence_after();
               const uint64_t db = umma_desc_sw128(b_ring_u32 + sb * B_STAGE_BYTES + j * BC * 128);
               const uint32_t d = tmem_base + buf * BC;
-              if constexpr (PAIR) {
+              if (issuer()) {
+                if constexpr (PAIR) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_f8_pair(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
-                umma_commit_pair(&S.tmem_full[buf]);
-              } else {
+                  for (int k = 0; k < 4; ++k) umma_f8_pair(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+                  umma_commit_pair(&S.tmem_full[buf]);
+                } else {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
-                umma_commit(&S.tmem_full[buf]);
+                  for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+                  umma_commit(&S.tmem_full[buf]);
+                }
               }
+              if constexpr (MONO_MMA_WARP != 0) __syncwarp();
               ++nt;
             }
             if (!ok) break;
-            if constexpr (PAIR) umma_commit_pair(&S.emptyB[sb]); else umma_commit(&S.emptyB[sb]);
+            if ((MONO_ABLATE & 64) == 0 && issuer()) { if constexpr (PAIR) umma_commit_pair(&S.emptyB[sb]); else umma_commit(&S.emptyB[sb]); }
+            if constexpr (MONO_MMA_WARP != 0) __syncwarp();
             ++nb;
+            TRACE_M(4);
           }
         }
 #ifdef MONO_PROFILE
         pm_total = clock64() - pm_start;
 #endif
-        PROF_STORE(1, pm_fullB); PROF_STORE(2, pm_fullA); PROF_STORE(3, pm_tmem); PROF_STORE(4, pm_inter);
-        PROF_STORE(5, pm_total);
-#ifdef MONO_PROFILE
-        for (int i = 0; i < 24; ++i) p.ws->prof[blockIdx.x][40 + i] = S.whist[1][i];
+        if (lane == 0) {
+          PROF_STORE(1, pm_fullB); PROF_STORE(2, pm_fullA); PROF_STORE(3, pm_tmem); PROF_STORE(4, pm_inter);
+          PROF_STORE(5, pm_total);
+        }
+#if defined(MONO_PROFILE) && !defined(MONO_TRACE)
+        if (lane == 0) for (int i = 0; i < 24; ++i) p.ws->prof[blockIdx.x][40 + i] = S.whist[1][i];
 #endif
       }
     } else {
@@ -1171,7 +1225,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       bool dead = false;  // after an abort: keep the loop structure (the named barrier stays matched), skip the work
       PROF_DECL(pg_emptyA);
       const uint32_t a_ring_u32 = smem_u32(a_ring);
-      for (int it = 0; it < n_my; ++it) {
+      for (int it = 0; it < ((MONO_ABLATE & 64) ? 0 : n_my); ++it) {
         const TileInfo ti = S.tiles[it];
         // the tile's 128 source tokens go through shared memory (two rows looked up per thread); the two
         // buffers alternate by tile, and the barrier of tile it+1 separates the last read of tile it-1's
@@ -1234,6 +1288,9 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       // Accumulators, pairs of adjacent columns. Buffer j of a slab owns acc[j*WC/2, (j+1)*WC/2):
       // first the HCB gate columns (down projection: the first half of WC output columns), then the up columns.
       float2 acc[TCOLS / 2];
+#if defined(MONO_TRACE) && defined(MONO_PROFILE)
+      int tr_e = 4000;
+#endif
       PROF_DECL(pe_bar); PROF_DECL(pe_zero); PROF_DECL(pe_wait); PROF_DECL(pe_up); PROF_DECL(pe_silu); PROF_DECL(pe_down); PROF_DECL(pe_store);
 #ifdef MONO_PROFILE
       const long long pe_start = clock64();
@@ -1250,34 +1307,6 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
           if (lane == 0) { if (PAIR && !leader) mbar_arrive_cluster(at_leader(&S.tmem_empty[buf])); else mbar_arrive(&S.tmem_empty[buf]); }
           return;
         }
-#if MONO_LDPIPE
-        // pieces of MONO_LDPIPE columns, the next piece in flight while this one is folded
-        {
-          constexpr int PW = MONO_LDPIPE, NPC = WC / PW;
-          uint32_t va[PW], vb[PW];
-          tmem_ld_n<PW>(t_lane + buf * BC, va);
-#pragma unroll
-          for (int c = 0; c < NPC; ++c) {
-            uint32_t (&cur)[PW] = (c & 1) ? vb : va;
-            uint32_t (&nxt)[PW] = (c & 1) ? va : vb;
-            tmem_ld_wait();
-            if (c + 1 < NPC) tmem_ld_n<PW>(t_lane + buf * BC + (c + 1) * PW, nxt);
-            if (c == NPC - 1) {
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) { if (PAIR && !leader) mbar_arrive_cluster(at_leader(&S.tmem_empty[buf])); else mbar_arrive(&S.tmem_empty[buf]); }
-            }
-#pragma unroll
-            for (int i = 0; i < PW / 2; ++i) {
-              const int pair = c * (PW / 2) + i;
-              const float sc = (pair < HCB / 2) ? s_lo : s_hi;
-              acc[j * (WC / 2) + pair] = __ffma2_rn(make_float2(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1])),
-                                                    make_float2(sc, sc), acc[j * (WC / 2) + pair]);
-            }
-          }
-          return;
-        }
-#endif
 #pragma unroll
         for (int c = 0; c < NLD; ++c) {
           uint32_t v[LDW];
@@ -1288,6 +1317,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) { if (PAIR && !leader) mbar_arrive_cluster(at_leader(&S.tmem_empty[buf])); else mbar_arrive(&S.tmem_empty[buf]); }
+            TRACE_E(2);
           }
 #pragma unroll
           for (int i = 0; i < LDW / 2; ++i) {
@@ -1390,12 +1420,15 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
 #pragma unroll
             for (int j = 0; j < NSPLIT; ++j) {
               const uint32_t buf = nt % NBUF;
+              TRACE_E(0);
               { PROF_T0();
               if (!dead && !mbar_wait(&S.tmem_full[buf], (nt / NBUF) & 1u, wc, kSiteTmemFull)) dead = true;
               PROF_ADD(pe_wait); PROF_HIST(0, (ks < 16 ? ks : 15), et == 0); }
+              TRACE_E(1);
               PROF_T0();
               if (!dead) promote(j, buf, s_g, s_u);
               PROF_ADD(pe_up);
+              TRACE_E(3);
               ++nt;
             }
           }
@@ -1441,7 +1474,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
 #pragma unroll
           for (int qq = 0; qq < NP; ++qq)
             if (qq == ps) iscale[qq] = my_scale;  // static indexing keeps the array in registers
-          uint8_t* irow = inter + ps * A_STAGE_BYTES;
+          uint8_t* irow = inter + (ps % INTER_SLOTS) * A_STAGE_BYTES;
 #pragma unroll
           for (int j = 0; j < ((MONO_ABLATE & 2) ? 0 : NSPLIT); ++j) {
 #pragma unroll
@@ -1485,12 +1518,15 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
               // output columns hb*256 + j*BC + h*WC ..: one [128,128] weight-scale block
               const float sc = __fmul_rn(wsd_t[(hb * 2 + (j * BC + h * WC) / 128) * NP + dk], iscale[dk]);
               const uint32_t buf = nt % NBUF;
+              TRACE_E(0);
               { PROF_T0();
               if (!dead && !mbar_wait(&S.tmem_full[buf], (nt / NBUF) & 1u, wc, kSiteTmemFull)) dead = true;
               PROF_ADD(pe_wait); PROF_HIST(0, 16 + dk, et == 0); }
+              TRACE_E(1);
               PROF_T0();
               if (!dead) promote(j, buf, sc, sc);
               PROF_ADD(pe_down);
+              TRACE_E(3);
               ++nt;
             }
           }
@@ -1538,7 +1574,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
       if (et == 0) {
         PROF_STORE(8, pe_wait); PROF_STORE(9, pe_up); PROF_STORE(10, pe_silu); PROF_STORE(11, pe_down);
         PROF_STORE(12, pe_store); PROF_STORE(14, pe_bar);
-#ifdef MONO_PROFILE
+#if defined(MONO_PROFILE) && !defined(MONO_TRACE)
         p.ws->prof[blockIdx.x][13] = static_cast<uint64_t>(clock64() - pe_start);
         for (int i = 0; i < 24; ++i) p.ws->prof[blockIdx.x][16 + i] = S.whist[0][i];
 #endif

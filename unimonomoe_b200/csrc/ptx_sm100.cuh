@@ -127,16 +127,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
       : "r"(taddr)
       : "memory");
 }
-// 16 consecutive columns per thread.
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr)
-      : "memory");
-}
 // 64 consecutive columns per thread.
 __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&v)[64]) {
   asm volatile(
@@ -159,9 +149,8 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&v)[64]) {
 }
 template <int N>
 __device__ __forceinline__ void tmem_ld_n(uint32_t taddr, uint32_t (&v)[N]) {
-  static_assert(N == 16 || N == 32 || N == 64, "16, 32 or 64 columns per load");
-  if constexpr (N == 16) tmem_ld16(taddr, v);
-  else if constexpr (N == 32) tmem_ld32(taddr, v);
+  static_assert(N == 32 || N == 64, "32 or 64 columns per load");
+  if constexpr (N == 32) tmem_ld32(taddr, v);
   else tmem_ld64(taddr, v);
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -216,6 +205,16 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+// One lane of the (fully converged) warp, chosen by the hardware: true in that lane only.
+__device__ __forceinline__ bool elect_one_sync() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xFFFFFFFF;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0u;
 }
 // The mbarrier receives one arrival once every tcgen05.mma issued so far by this
 // thread has completed (implies tcgen05.fence::before_thread_sync).
