@@ -1656,9 +1656,13 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
     // the peer's window when the group has two ranks and the caller passed the table of windows
     __nv_bfloat16* const peer_pair = (tp_on && p.tp_peers != nullptr && p.tp_world == 2) ? p.tp_peers[1 - p.tp_rank] : nullptr;
     // Whole CTA: take pieces of this rank's share of chunk c until none is left. False when the launch aborts.
+    // Waits that end only when another bounded wait of this launch has ended (a chunk is opened behind a rank
+    // barrier; the closer waits for every piece) get twice the limit, so that the status word names the wait
+    // that actually ran out, not one queued behind it.
+    const WaitCtx wc_dep{p.ws, 2 * p.timeout_ns};
     auto reduce_pieces = [&](int c) -> bool {
       if (tid == 0)
-        S.flag = wait_counter_ge(&ws->tp_open[c], 1u, wc, kErrChunkReady, static_cast<uint32_t>(16 + c)) ? 1u : 0u;
+        S.flag = wait_counter_ge(&ws->tp_open[c], 1u, wc_dep, kErrChunkReady, static_cast<uint32_t>(16 + c)) ? 1u : 0u;
       __syncthreads();
       const bool open = S.flag != 0u;
       __syncthreads();
@@ -1838,7 +1842,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
           share_of(c, s_lo, s_hi);
           total += static_cast<uint32_t>((s_hi - s_lo + PIECE - 1) / PIECE);
         }
-        if (wait_counter_ge(&ws->tp_pieces_done, total, wc, kErrDoneFlag, 0) && rank_barrier(nchunk * p.tp_ncomm)) {
+        if (wait_counter_ge(&ws->tp_pieces_done, total, wc_dep, kErrDoneFlag, 0) && rank_barrier(nchunk * p.tp_ncomm)) {
           __threadfence();
           atomicExch(&ws->tp_done_flag, 1u);
         }
