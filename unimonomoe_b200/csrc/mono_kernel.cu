@@ -69,6 +69,7 @@
 // results are then wrong) so that its share of the run time can be measured by difference.
 //   1: no TMEM read-out / promotion   2: no SiLU / requantisation arithmetic   4: no partial-row stores
 //   8: no activation gather copies    16: no weight TMA loads
+//   128: every slab step issues its four MMAs twice (1024 tensor-core cycles per step: is a step bound by latency or by issue?)
 //   64: no operand hand-shake at all (producers idle; the MMA warp waits only for accumulator buffers)
 //   32: the intermediate's passes alias one 16 KB slot, which leaves room for four-deep operand rings
 #ifndef MONO_ABLATE
@@ -1133,7 +1134,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
                   umma_commit_pair(&S.tmem_full[buf]);
                 } else {
 #pragma unroll
-                  for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+                  for (int k = 0; k < ((MONO_ABLATE & 128) ? 8 : 4); ++k) umma_f8(d, da + 2u * (k & 3), db + 2u * (k & 3), IDESC, k > 0 ? 1u : 0u);
                   umma_commit(&S.tmem_full[buf]);
                 }
               }
@@ -1185,7 +1186,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
                   umma_commit_pair(&S.tmem_full[buf]);
                 } else {
 #pragma unroll
-                  for (int k = 0; k < 4; ++k) umma_f8(d, da + 2u * k, db + 2u * k, IDESC, k > 0 ? 1u : 0u);
+                  for (int k = 0; k < ((MONO_ABLATE & 128) ? 8 : 4); ++k) umma_f8(d, da + 2u * (k & 3), db + 2u * (k & 3), IDESC, k > 0 ? 1u : 0u);
                   umma_commit(&S.tmem_full[buf]);
                 }
               }
