@@ -359,20 +359,39 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    mk.check_status(sc["workspace"])
-
-    parity = None
-    if world > 1 and not args.no_verify:
+    def warm_up_and_verify():
+        """Warm-up steps, the device status of every rank, then the parity check of what is about to be timed.
+        Returns (parity or None, reason the configuration must not be timed or None); the same on every rank."""
+        for _ in range(args.warmup):
+            step()
+        barrier()
+        why = uniform_status(mk, sc["workspace"], world, dist, dev)
+        if why is not None and world == 1:
+            raise RuntimeError(why)
+        if why is not None or world == 1 or args.no_verify:
+            return None, why
         result_now = plan.pool.output(T) if plan is not None else out
-        parity = verify_reduced_output(spec, mk, layer, batch, emap, sc, pool_plan, result_now, world, rank, dist, dev,
-                                       par, kw, fused=plan is not None)
-        if not parity["ok"]:
-            if rank == 0:
-                print(json.dumps({"metric": METRIC, "parity_checked": False, "parity": parity}), flush=True)
-            raise SystemExit(3)
+        par_info = verify_reduced_output(spec, mk, layer, batch, emap, sc, pool_plan, result_now, world, rank, dist,
+                                         dev, par, kw, fused=plan is not None)
+        return par_info, (None if par_info["ok"] else "parity check failed")
+
+    reduce_fallback = None
+    parity, why = warm_up_and_verify()
+    if why is not None and plan is not None and args.reduce == "auto" and not args.unfused:
+        # the in-kernel reduce was chosen by the table, not asked for: say what happened and time the launch
+        # followed by NCCL instead, behind the same check (a launch that gave up a wait leaves the status word set
+        # for the host to read and returns; the next launch starts clean)
+        reduce_fallback = {"from": reduce_desc, "why": why, "parity": parity}
+        if rank == 0:
+            print(f"# in-kernel reduce rejected ({why}); timing kernel + NCCL all-reduce instead", file=sys.stderr)
+        plan = None
+        reduce_desc = "NCCL all-reduce after the kernel"
+        parity, why = warm_up_and_verify()
+    if why is not None:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "parity_checked": False, "why": why, "parity": parity,
+                              "reduce_fallback": reduce_fallback}), flush=True)
+        raise SystemExit(3)
 
     # ---- device-resident timing: K steps between two events, plus one event pair per kernel launch
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
@@ -434,7 +453,7 @@ def main() -> None:
         phases = [round((ph[i + 1] - ph[i]) / 1e3, 1) for i in range(4)]
         stall_counters(mk, sc["workspace"])
         report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
-               reduce_desc, phases, sustained, parity, with_shared, extra)
+               reduce_desc, phases, sustained, parity, with_shared, extra, reduce_fallback)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -662,6 +681,23 @@ def sweep_reduce_shapes(spec_text, plan, T, launch, batch, barrier, dist, dev, m
     plan.chunks_by_tokens[T], plan.ncomm = keep
 
 
+def uniform_status(mk, workspace, world, dist, dev):
+    """The kernel's status word of this rank's last launch, agreed over the ranks: None when every rank's launch
+    ended cleanly, else a reason (this rank's own, or that another rank reported one). Never raises, so that
+    every rank takes the same branch after it."""
+    why = None
+    try:
+        mk.check_status(workspace)
+    except RuntimeError as e:
+        why = str(e)
+    if world > 1:
+        flag = torch.tensor([0 if why is None else 1], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        if int(flag.item()) and why is None:
+            why = "device status of another rank"
+    return why
+
+
 def time_other_split(model, world, rank, dist, dev, barrier, T, steps=10) -> dict:
     """One more configuration timed in the same process after the contract's own: the tensor-parallel split of
     the Qwen-like layer (4 GPUs) or of the DeepSeek-V3-like layer (8 GPUs), reduce inside the kernel, behind the
@@ -686,7 +722,9 @@ def time_other_split(model, world, rank, dist, dev, barrier, T, steps=10) -> dic
     for _ in range(3):
         go()
     barrier()
-    mk.check_status(sc["workspace"])
+    why = uniform_status(mk, sc["workspace"], world, dist, dev)
+    if why is not None:
+        return {"variant": variant, "tokens": T, "failed": why}
     parity = verify_reduced_output(spec, mk, layer, batch, None, sc, plan, plan.pool.output(T), world, rank, dist, dev,
                                    f"tp{world}", kw, fused=True)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -696,7 +734,9 @@ def time_other_split(model, world, rank, dist, dev, barrier, T, steps=10) -> dic
         go()
     e1.record()
     barrier()
-    mk.check_status(sc["workspace"])
+    why = uniform_status(mk, sc["workspace"], world, dist, dev)
+    if why is not None:
+        return {"variant": variant, "tokens": T, "failed": why}
     t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t[0])
@@ -845,7 +885,8 @@ def verify_reduced_output(spec, mk, layer, batch, emap, sc, pool_plan, result, w
 
 
 def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
-           reduce_desc, phases=None, sustained=None, parity=None, with_shared=None, extra=None) -> None:
+           reduce_desc, phases=None, sustained=None, parity=None, with_shared=None, extra=None,
+           reduce_fallback=None) -> None:
     peaks = measured_peaks()
     fp8_lib = fp8_gemm_tflops(dev) if (world == 1 and not args.kernel_only) else None
     if peaks.get("bf16_tflops"):
@@ -901,6 +942,8 @@ def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flop
         line["extra"] = extra
     if world > 1:
         line["parity_checked"] = bool(parity is not None and parity["ok"])
+        if reduce_fallback is not None:
+            line["reduce_fallback"] = reduce_fallback
         line["parity"] = parity
     if world == 1 and not args.no_cpu_baseline and not args.kernel_only:
         line["cpu_baseline"] = time_cpu_baseline(spec, REFERENCE_SAMPLE_TOKENS)
