@@ -51,7 +51,7 @@ VARIANTS = {
 DEV_VARIANTS = {
     "qwen_w1_prof": dict(QWEN, N_HALF=512, E_LOCAL=256, PROFILE=1),
     "qwen_w1_trace": dict(QWEN, N_HALF=512, E_LOCAL=256, PROFILE=1, DEFS=("MONO_TRACE",)),
-    **{f"qwen_w1_abl{m}": dict(QWEN, N_HALF=512, E_LOCAL=256, ABLATE=m) for m in (1, 4, 7, 15, 23, 31, 39, 71, 199)},
+    **{f"qwen_w1_abl{m}": dict(QWEN, N_HALF=512, E_LOCAL=256, ABLATE=m) for m in (1, 4, 7, 15, 23, 31, 39, 71, 199, 256)},
 }
 
 SOURCES = ["mono_kernel.cu", "ptx_sm100.cuh", "pair_sm100.cuh", "bounded_wait.cuh", "route_math.cuh"]

@@ -69,6 +69,7 @@
 // results are then wrong) so that its share of the run time can be measured by difference.
 //   1: no TMEM read-out / promotion   2: no SiLU / requantisation arithmetic   4: no partial-row stores
 //   8: no activation gather copies    16: no weight TMA loads
+//   256: no lane exchange before the partial-row stores (same bytes, wrong columns)
 //   128: every slab step issues its four MMAs twice (1024 tensor-core cycles per step: is a step bound by latency or by issue?)
 //   64: no operand hand-shake at all (producers idle; the MMA warp waits only for accumulator buffers)
 //   32: the intermediate's passes alias one 16 KB slot, which leaves room for four-deep operand rings
@@ -1558,7 +1559,7 @@ __global__ void __launch_bounds__(BLOCK, 1) moe_prefill_kernel(const __grid_cons
                 for (int i = 0; i < 8; ++i) {
                   // an even lane keeps its piece 2*k2 and gives away 2*k2+1; an odd lane the other way round
                   const uint32_t send = odd ? lo[i] : hi[i];
-                  theirs[i] = __shfl_xor_sync(0xFFFFFFFFu, send, 1);
+                  theirs[i] = (MONO_ABLATE & 256) ? send : __shfl_xor_sync(0xFFFFFFFFu, send, 1);
                   mine[i] = odd ? hi[i] : lo[i];
                 }
                 const int piece = 2 * k2 + (odd ? 1 : 0);
