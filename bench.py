@@ -648,11 +648,11 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barr
 
 
 # (model, split, ranks) -> is the reduce inside the kernel faster than NCCL after it? Measured on B200 at
-# T=16384 (expert-parallel Qwen-like layer, us per layer in-kernel / NCCL): 2 ranks 597 / 625, 4 ranks 491 / 513,
-# 8 ranks 421 / 626. A split that is not listed takes the in-kernel reduce.
+# T=16384 (expert-parallel Qwen-like layer, us per layer in-kernel / NCCL): 2 ranks 597-602 / 625-632, 4 ranks
+# 491-496 / 513-516, 8 ranks 402-420 / 514. A split that is not listed takes the in-kernel reduce.
 FUSED_REDUCE_WINS = {("qwen", "ep", 2): True, ("qwen", "ep", 4): True, ("qwen", "ep", 8): True}
 # ranks -> (chunks, communication CTAs) of the in-kernel reduce at T = 16384 (half the chunks at smaller T)
-REDUCE_SHAPES = {2: (2, 32), 4: (4, 16), 8: (8, 32)}
+REDUCE_SHAPES = {2: (2, 32), 4: (4, 16), 8: (4, 32)}   # 8 ranks: 4 chunks 402 us, 8 chunks 416, 16 chunks 459
 
 
 def sweep_reduce_shapes(spec_text, plan, T, launch, batch, barrier, dist, dev, mk, sc, rank) -> None:
