@@ -448,12 +448,32 @@ def main() -> None:
     h2d = batch["hs"].numel() * 2 + (batch["logits"].numel() * 4 if rw16 is None else 0)
     d2h = out.numel() * 2
 
-    if rank == 0:
+    phases = None
+    if rank == 0:   # of the contract's own launch, before anything else runs through this workspace
         ph = mk.workspace_view(sc["workspace"])["phase_ns"].tolist()
         phases = [round((ph[i + 1] - ph[i]) / 1e3, 1) for i in range(4)]
         stall_counters(mk, sc["workspace"])
+
+    e2e_router_inside = None
+    if world == 1 and not args.kernel_only and rw16 is None and args.model == "qwen" and args.variant is None and mk.has_gemv:
+        # the same step with the router linear inside the launch (the gate weight stays on the device like every
+        # other weight): only the hidden states cross PCIe, the logits are computed, not uploaded
+        rw_in = layer["router_w"].to(torch.bfloat16).contiguous()
+
+        def launch_gemv(hs, lg, dst=None):
+            mk.prefill_impl(hs, lg, layer["w13"], layer["w13_scale"], layer["w2"], layer["w2_scale"], spec.top_k, True,
+                            layer["bias"], out if dst is None else dst, expert_map=emap, scratch=sc, router_weight=rw_in)
+        g_ms = time_e2e(args, spec, batch, out, launch_gemv, reduce_out, world, rank, dist, barrier, dev,
+                        with_logits=False, second_out=torch.empty_like(out))
+        mk.check_status(sc["workspace"])
+        e2e_router_inside = {"value": flops / (g_ms[0] * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": g_ms[0],
+                             "serial_ms_per_step": g_ms[1], "h2d_bytes_per_step": batch["hs"].numel() * 2,
+                             "d2h_bytes_per_step": d2h,
+                             "entry": "launch_prefill_moe_wgmma_q1_gemv: logits = x . W_r^T computed in phase R of the same launch"}
+
+    if rank == 0:
         report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
-               reduce_desc, phases, sustained, parity, with_shared, extra, reduce_fallback)
+               reduce_desc, phases, sustained, parity, with_shared, extra, reduce_fallback, e2e_router_inside)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -886,7 +906,7 @@ def verify_reduced_output(spec, mk, layer, batch, emap, sc, pool_plan, result, w
 
 def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flops, e2e_ms, h2d, d2h, clk, dev,
            reduce_desc, phases=None, sustained=None, parity=None, with_shared=None, extra=None,
-           reduce_fallback=None) -> None:
+           reduce_fallback=None, e2e_router_inside=None) -> None:
     peaks = measured_peaks()
     fp8_lib = fp8_gemm_tflops(dev) if (world == 1 and not args.kernel_only) else None
     if peaks.get("bf16_tflops"):
@@ -940,6 +960,8 @@ def report(args, spec, T, world, par, variant, value, ms_per_step, kern_ms, flop
         line["with_shared_expert"] = with_shared
     if extra is not None:
         line["extra"] = extra
+    if e2e_router_inside is not None and line["e2e"] is not None:
+        line["e2e"]["router_inside"] = e2e_router_inside
     if world > 1:
         line["parity_checked"] = bool(parity is not None and parity["ok"])
         if reduce_fallback is not None:
