@@ -9,7 +9,10 @@ experts per rank, all tokens on every rank) with the ranks' partial outputs redu
 kernel or by NCCL after it, whichever was measured faster for that N (--reduce overrides;
 --parallel tp selects the tensor-parallel split, --model deepseek the DeepSeek-V3-like layer).
 Before anything is timed at N>1 the reduced output of exactly that configuration is checked
-against an unfused launch + all-reduce and against the CPU oracle. Prints ONE JSON line (rank 0).
+against an unfused launch + all-reduce and against the CPU oracle; when the in-kernel reduce was chosen by
+the table (not by --reduce fused) and fails that check or leaves a device status, the line says so
+(`reduce_fallback`) and kernel + NCCL is checked and timed instead (BENCH_INJECT_FUSED_REJECT=1 exercises
+that branch from the host). Prints ONE JSON line (rank 0).
 --impl reference times the reference's CPU path (torch MoE on dequantised weights, host cores)
 on a bounded sample of the same workload.
 """
@@ -377,6 +380,8 @@ def main() -> None:
 
     reduce_fallback = None
     parity, why = warm_up_and_verify()
+    if os.environ.get("BENCH_INJECT_FUSED_REJECT") == "1" and plan is not None and why is None:
+        why = "injected by BENCH_INJECT_FUSED_REJECT (host-side test of the fallback)"
     if why is not None and plan is not None and args.reduce == "auto" and not args.unfused:
         # the in-kernel reduce was chosen by the table, not asked for: say what happened and time the launch
         # followed by NCCL instead, behind the same check (a launch that gave up a wait leaves the status word set
