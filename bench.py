@@ -253,9 +253,12 @@ def main() -> None:
     ap.add_argument("--router", default="logits", choices=["logits", "gemv"],
                     help="logits: the caller's router logits go in (the reference's interface); gemv: the bf16 gate "
                          "weight goes in and the router linear runs inside the launch (no logits cross PCIe in e2e)")
-    ap.add_argument("--gather", default="nccl", choices=["nccl", "multimem"],
+    ap.add_argument("--gather", default="nccl", choices=["nccl", "multimem", "ce"],
                     help="N>1, e2e leg: how the row shards uploaded by the ranks are completed on every GPU: NCCL "
-                         "all-gather, or multimem stores into symmetric buffers (measured equal at 2 GPUs)")
+                         "all-gather, multimem stores into symmetric buffers (measured equal at 2 GPUs), or 'ce': every "
+                         "rank pushes its rows into the peers' symmetric buffers with copy-engine copies and the ranks "
+                         "signal each other with stream-ordered 32-bit writes and waits, so that nothing of the "
+                         "exchange needs an SM while the persistent kernel holds them all")
     ap.add_argument("--variant", default=None,
                     help="N=1 only: time another binary of the same geometry, e.g. a development build made with "
                          "`python -m unimonomoe_b200.build qwen_w1_prof` (stall counters) or qwen_w1_abl7 (a piece of "
@@ -510,6 +513,92 @@ def stall_counters(mk, workspace) -> None:
               + " | down " + " ".join(f"{v:.1f}" for v in h[16:20].tolist()), file=sys.stderr)
 
 
+class _CopyEngineGather:
+    """All-gather of the ranks' uploaded row shards without any kernel: symmetric input buffers (two slots), every
+    rank copies its rows into each peer's buffer with device-to-device copies (copy engines), then raises a
+    counter in the peer's memory with a stream-ordered 32-bit write; the consumer's stream waits on those counters
+    with a stream-ordered wait. A second set of counters tells the producers that a slot has been read (the kernel
+    that used it is finished) before it is overwritten. Counters only grow (use number of the slot)."""
+
+    def __init__(self, batch, rows, nb, world, rank, dist, dev, with_logits):
+        self.ok, self.why = False, ""
+        self.rows, self.nb, self.world, self.rank, self.with_logits = rows, nb, world, rank, with_logits
+        self.use = [0] * nb
+        try:
+            import torch.distributed._symmetric_memory as sm
+            from cuda.bindings import driver as drv
+            self.drv = drv
+            gname = dist.group.WORLD.group_name
+            self.hs = [sm.empty(batch["hs"].shape, dtype=batch["hs"].dtype, device=dev) for _ in range(nb)]
+            self.lg = [sm.empty(batch["logits"].shape, dtype=batch["logits"].dtype, device=dev) for _ in range(nb)]
+            self.flags = sm.empty((2 * nb * world + 1,), dtype=torch.uint32, device=dev)   # + one word for the self-test
+            self.flags.view(torch.int32).zero_()
+            torch.cuda.synchronize()
+            h_hs = [sm.rendezvous(t, gname) for t in self.hs]
+            h_lg = [sm.rendezvous(t, gname) for t in self.lg]
+            self.h_flags = sm.rendezvous(self.flags, gname)
+            peers = [p for p in range(world) if p != rank]
+            self.peers = peers
+            self.hs_peer = [{p: h_hs[b].get_buffer(p, batch["hs"].shape, batch["hs"].dtype) for p in peers} for b in range(nb)]
+            self.lg_peer = [{p: h_lg[b].get_buffer(p, batch["logits"].shape, batch["logits"].dtype) for p in peers} for b in range(nb)]
+            self.flags_peer = {p: self.h_flags.get_buffer(p, (2 * nb * world + 1,), torch.uint32) for p in peers}
+            self.flags_flat = self.flags.view(-1)
+            # self-test of the two stream memory operations on this rank's own word (already satisfied wait)
+            last = 2 * nb * world
+            self.h_flags.stream_write_value32(self.flags_flat, last, 7)
+            cur = torch.cuda.current_stream()
+            (err,) = drv.cuStreamWaitValue32(drv.CUstream(cur.cuda_stream), drv.CUdeviceptr(self.flags_flat.data_ptr() + 4 * last),
+                                             7, drv.CUstreamWaitValue_flags.CU_STREAM_WAIT_VALUE_GEQ)
+            torch.cuda.synchronize()
+            if int(err) != 0 or int(self.flags_flat.view(torch.int32)[last].item()) != 7:
+                raise RuntimeError(f"stream memory operations not usable here (err {err})")
+            dist.barrier()
+            self.ok = True
+        except Exception as ex:  # noqa: BLE001 - any failure means "use the NCCL path"
+            self.why = f"{type(ex).__name__}: {ex}"
+
+    def _idx(self, kind, b, src):
+        return (kind * self.nb + b) * self.world + src
+
+    def _wait(self, stream, kind, b, value):
+        drv = self.drv
+        for p in self.peers:
+            addr = self.flags_flat.data_ptr() + 4 * self._idx(kind, b, p)
+            (err,) = drv.cuStreamWaitValue32(drv.CUstream(stream.cuda_stream), drv.CUdeviceptr(addr), value,
+                                             drv.CUstreamWaitValue_flags.CU_STREAM_WAIT_VALUE_GEQ)
+            if int(err) != 0:
+                raise RuntimeError(f"cuStreamWaitValue32 failed: {err}")
+
+    def _signal(self, kind, b, value):
+        for p in self.peers:     # on the current stream, behind the copies / the kernel
+            self.h_flags.stream_write_value32(self.flags_peer[p], self._idx(kind, b, self.rank), value)
+
+    def begin(self, b, stream) -> int:
+        """Next use of slot b: wait until every peer has read its previous contents. Returns the use number."""
+        self.use[b] += 1
+        u = self.use[b]
+        if u > 1:
+            self._wait(stream, 1, b, u - 1)
+        return u
+
+    def upload_and_push(self, b, hs_host, lg_host, u) -> None:
+        rows = self.rows
+        self.hs[b][rows].copy_(hs_host, non_blocking=True)
+        if self.with_logits:
+            self.lg[b][rows].copy_(lg_host, non_blocking=True)
+        for p in self.peers:
+            self.hs_peer[b][p][rows].copy_(self.hs[b][rows], non_blocking=True)
+            if self.with_logits:
+                self.lg_peer[b][p][rows].copy_(self.lg[b][rows], non_blocking=True)
+        self._signal(0, b, u)
+
+    def wait_full(self, b, stream, u) -> None:
+        self._wait(stream, 0, b, u)
+
+    def release(self, b, u) -> None:
+        self._signal(1, b, u)
+
+
 def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barrier, dev, with_logits=True,
              second_out=None) -> tuple:
     """End to end through the public API: host buffers in, host result out, every step's copies inside the
@@ -556,7 +645,19 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barr
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)   # every rank must take the same path
         if int(ok.item()) == 0:
             gather_kind = "nccl"
-    if gather_kind != "multimem":
+    ce = None
+    if world > 1 and args.gather == "ce":
+        ce = _CopyEngineGather(batch, rows, NB, world, rank, dist, dev, with_logits)
+        ok = torch.tensor([1 if ce.ok else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            if rank == 0:
+                print(f"# copy-engine all-gather unavailable ({ce.why}); using NCCL", file=sys.stderr)
+            ce = None
+        else:
+            gather_kind = "ce"
+            hs_dev, lg_dev = ce.hs, ce.lg
+    if gather_kind not in ("multimem", "ce"):
         hs_dev = [torch.empty_like(batch["hs"]) for _ in range(NB)]
         lg_dev = [torch.empty_like(batch["logits"]) for _ in range(NB)]
     hs_part = [torch.empty_like(batch["hs"][rows]) for _ in range(NB)] if world > 1 else None
@@ -588,6 +689,15 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barr
                 dist.all_gather_into_tensor(lg_dev[b], lg_part[b])
 
     def serial_step():
+        if ce is not None:
+            u = ce.begin(0, cur)
+            ce.upload_and_push(0, hs_host, lg_host, u)
+            ce.wait_full(0, cur, u)
+            launch(hs_dev[0], lg_dev[0], outs[0])
+            reduce_out(outs[0])
+            ce.release(0, u)
+            out_host[0].copy_(outs[0][rows], non_blocking=True)
+            return
         upload(0)
         gather(0)
         launch(hs_dev[0], lg_dev[0], outs[0])
@@ -596,6 +706,25 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barr
 
     def piped_step(i):
         b, o = i % NB, i % len(outs)
+        if ce is not None:
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_k[b])
+                u = ce.begin(b, s_in)
+                ce.upload_and_push(b, hs_host, lg_host, u)
+                ev_in[b].record(s_in)
+            with torch.cuda.stream(s_c):
+                s_c.wait_event(ev_in[b])
+                s_c.wait_event(ev_o[o])
+                ce.wait_full(b, s_c, u)
+                launch(hs_dev[b], lg_dev[b], outs[o])
+                reduce_out(outs[o])
+                ev_k[b].record(s_c)
+                ce.release(b, u)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_k[b])
+                out_host[o].copy_(outs[o][rows], non_blocking=True)
+                ev_o[o].record(s_out)
+            return
         with torch.cuda.stream(s_in):
             s_in.wait_event(ev_k[b])
             upload(b)
@@ -660,7 +789,7 @@ def time_e2e(args, spec, batch, out, launch, reduce_out, world, rank, dist, barr
     account = {"host_enqueue_ms_per_step": host_enqueue_ms, "h2d_alone_ms": alone(lambda: upload(0)),
                "d2h_alone_ms": alone(lambda: out_host[0].copy_(outs[0][rows], non_blocking=True))}
     gather_ms = 0.0
-    if world > 1:   # the all-gather alone, for the record
+    if world > 1 and ce is None:   # the all-gather alone, for the record
         g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         g0.record()
